@@ -156,6 +156,48 @@ int lb_prefill_attention_tc(const void* q, int64_t q_stride, int n_tokens, const
                             int page_size, float scale, int window, void* stream);
 int lb_prefill_attention_tc_supports(int n_head, int n_kv_head, int head_dim, int page_size);
 
+/* y[r,:] = x[rows ? rows[r] : r, :] cut into `groups` equal consecutive parts, each divided by its own
+ * sqrt(mean(part^2) + eps), the whole times weight (float, may be null); statistics in 32-bit; y is `out_dtype`. */
+int lb_rms_groups(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, void* y, int64_t ldy,
+                  int n_rows, int width, int groups, float eps, void* stream);
+/* Token shift: m[t] = h[t] + (prev - h[t]) * mix, where prev is h[t - 1] within a request's run of rows and the
+ * request's state (row slots[s] of `state`, [slot, width] of `dtype`) for the run's first row; afterwards the state
+ * holds the run's last row of h.  tok_seq[t] is the request of row t, q_start[s] .. q_start[s + 1] - 1 its rows.
+ * decode_only: every request brings one row (the second launch, which saves longer runs' last rows, is left out). */
+int lb_token_shift(int dtype, const void* h, int64_t ldh, const float* mix, void* m, int64_t ldm, void* state,
+                   const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, int n_tokens, int n_seq, int decode_only,
+                   int width, void* stream);
+/* lb_rms_groups (to h) and lb_token_shift (to m) in one pass over the float rows x. */
+int lb_rms_shift(int dtype, const float* x, int64_t ldx, const float* weight, const float* mix, void* h, int64_t ldh, void* m,
+                 int64_t ldm, void* state, const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, int n_tokens,
+                 int n_seq, int decode_only, int width, int groups, float eps, void* stream);
+/* In place: z > 0 -> a z^2 + z/2, else b (exp(z) - 1 - z) + z/2, a = softplus(pq[0]), b = 1/2 + softplus(pq[1]). */
+int lb_xielu(int dtype, void* z, int64_t ldz, int n_rows, int cols, const float* pq, void* stream);
+/* x[t,:] += rms(y) * weight with y = proj . (gelu_tanh(gate . x[t,:]) * table[tokens[t],:]); gate [dim, width], proj
+ * [width, dim] and table [vocab, dim] are `dtype`, x and weight float; rms divides by sqrt(mean(y^2) + eps). */
+int lb_token_side(int dtype, float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* gate, const void* proj,
+                  const float* weight, int n_tokens, int width, int dim, float eps, void* stream);
+
+/* Attention over a cache of latent rows [c (rank) | r (rot)], one row per position: pages [page][slot][rank + rot].
+ * lb_latent_store: row t of d (float, [rank | rot]) -> c = d[:rank] / sqrt(mean^2 + eps) * gain; r = the last rot values
+ * with the first rot_dims of them rotated (value i pairs with i + rot_dims/2, angle position * freq[i]); written at
+ * slot_mapping[t] (negative: nowhere). */
+int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
+                    const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps, void* stream);
+/* Queries [T, H * (dim + rot)], head by head [dim | rot]: the rot part, rotated as above, goes to columns
+ * h * (rank + rot) + rank .. of the wide queries (float). */
+int lb_rope_heads(int q_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, float* wide, int64_t ldw,
+                  int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, void* stream);
+/* C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n], n < N, k < K, for every head h;
+ * 32-bit FMA whatever the element types (built: f32 f32 f32; bf16 bf16 f32; f32 bf16 bf16; f32 bf16 f32). */
+int lb_head_matmul(int a_dtype, int b_dtype, int c_dtype, const void* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head,
+                   int64_t b_k, int64_t b_n, void* C, int64_t ldc, int64_t c_head, int M, int N, int K, int n_head, void* stream);
+/* out[t, h * rank + :] = sum_j p_j c_j with p = softmax_j((wide[t, h, :] . row_j) * scale) over the rows j of the token's
+ * request with 0 <= position - j < window (window 0: all j <= position). */
+int lb_latent_attention(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
+                        const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
+                        int n_head, int rank, int rot, int page_size, float scale, int window, void* stream);
+
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw
  * uniform[r] in [0,1).  out_probs (optional, [n_rows, vocab]) receives the

@@ -1,0 +1,310 @@
+// Attention over a cache of latent rows.
+//
+// A position's cache row is [c | r]: a latent c of `rank` values, from which every head's keys and values are
+// linear maps (k_h = U_h c, v_h = V_h c), and one rotated key part r of `rot` values shared by all heads.  The
+// maps are moved to the query's side, so that attention runs on the cache rows as they are:
+//     score_h(i, j) = ((U_h^T q_h) . c_j + q'_h . r_j) * scale,      out_h(i) = V_h (sum_j p_h(i, j) c_j)
+// with q_h the unrotated and q'_h the rotated part of head h's query.  The pieces:
+//   lb_latent_store    d = [rank | rot] per token -> RMS norm of the first part, rotation of the second, into the pages
+//   lb_rope_heads      rotation of the queries' rotated parts into the wide queries [T, H, rank + rot]
+//   lb_head_matmul     a product per head (U_h^T q_h into the wide queries; V_h on the attended latents)
+//   lb_latent_attention  softmax attention of wide queries over the rows, causal, optionally windowed
+// All arithmetic here is 32-bit (FMA units); the element type only says how rows and weights are stored.
+// Summation orders depend on a token's position only, never on the batch or on how a sequence was cut.
+#include "api.h"
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+// The pair (u, v) = (x[i], x[i + half]) at angle a = position * freq[i] becomes (u cos a - v sin a, v cos a + u sin a).
+__device__ __forceinline__ void rotate_pair(float u, float v, int position, float freq, float* ru, float* rv) {
+    float sn, cs;
+    sincosf((float)position * freq, &sn, &cs);
+    *ru = u * cs - v * sn;
+    *rv = v * cs + u * sn;
+}
+
+template <typename T>
+__global__ void latent_store_kernel(const float* __restrict__ d, int64_t ldd, const float* __restrict__ gain, const float* __restrict__ freq,
+                                    const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, T* __restrict__ cache,
+                                    int rank, int rot, int rot_dims, float eps) {
+    __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const float* in = d + (size_t)t * ldd;
+    T* out = cache + (size_t)slot * (rank + rot);
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)rank + eps);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = lb_from_float<T>(in[i] * inv * gain[i]);
+    const int half = rot_dims / 2, p = positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float u, v;
+        rotate_pair(in[rank + i], in[rank + half + i], p, freq[i], &u, &v);
+        out[rank + i] = lb_from_float<T>(u);
+        out[rank + half + i] = lb_from_float<T>(v);
+    }
+    for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = lb_from_float<T>(in[rank + i]);
+}
+
+// q: [T, H * (dim + rot)], head by head [dim | rot]; wide: [T, H * (rank + rot)] float, head by head [rank | rot].
+template <typename T>
+__global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const float* __restrict__ freq, const int32_t* __restrict__ positions,
+                                  float* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims, int rank) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, p = positions[t], half = rot_dims / 2;
+    const int keep = rot - rot_dims, per_head = half + keep;
+    for (int idx = threadIdx.x; idx < n_head * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, i = idx - h * per_head;
+        const T* in = q + (size_t)t * ldq + (size_t)h * (dim + rot) + dim;
+        float* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot) + rank;
+        if (i < half) {
+            float u, v;
+            rotate_pair(lb_to_float(in[i]), lb_to_float(in[half + i]), p, freq[i], &u, &v);
+            out[i] = u;
+            out[half + i] = v;
+        } else {
+            out[rot_dims + i - half] = lb_to_float(in[rot_dims + i - half]);
+        }
+    }
+}
+
+// C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n] for n < N, k < K.
+// Tiles of 32 rows x 64 columns, K in chunks of 32 added in ascending order: a row's sums do not depend on the batch.
+template <typename TA, typename TB, typename TC>
+__global__ void __launch_bounds__(256)
+head_matmul_kernel(const TA* __restrict__ A, int64_t lda, int64_t a_head, const TB* __restrict__ B, int64_t b_head, int64_t b_k, int64_t b_n,
+                   TC* __restrict__ C, int64_t ldc, int64_t c_head, int M, int N, int K) {
+    __shared__ float As[32][33];
+    __shared__ float Bs[32][65];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int h = blockIdx.z, m0 = blockIdx.y * 32, n0 = blockIdx.x * 64;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const TA* a = A + (size_t)h * a_head;
+    const TB* b = B + (size_t)h * b_head;
+    float acc[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        for (int idx = threadIdx.x; idx < 32 * 32; idx += 256) {
+            const int r = idx >> 5, k = idx & 31;
+            As[r][k] = (m0 + r < M && k0 + k < K) ? lb_to_float(a[(size_t)(m0 + r) * lda + k0 + k]) : 0.0f;
+        }
+        if (b_n == 1) {
+            for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+                const int k = idx >> 6, n = idx & 63;
+                Bs[k][n] = (k0 + k < K && n0 + n < N) ? lb_to_float(b[(size_t)(k0 + k) * b_k + (n0 + n)]) : 0.0f;
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+                const int n = idx >> 5, k = idx & 31;
+                Bs[k][n] = (k0 + k < K && n0 + n < N) ? lb_to_float(b[(size_t)(k0 + k) * b_k + (size_t)(n0 + n) * b_n]) : 0.0f;
+            }
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float bv = Bs[k][tx + 16 * j];
+                acc[0][j] = fmaf(a0, bv, acc[0][j]);
+                acc[1][j] = fmaf(a1, bv, acc[1][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = m0 + ty * 2 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n < N) C[(size_t)r * ldc + (size_t)h * c_head + n] = lb_from_float<TC>(acc[i][j]);
+        }
+    }
+}
+
+// One block per (token, group of four heads), one warp per head.  The token's visible rows, from the first visible
+// position in steps of 32, are staged as floats in shared memory once for the four heads; lane j of a warp makes the
+// score of row j, the warp keeps a running softmax over the steps, and every lane owns the latent's values
+// lane, lane + 32, ... of the weighted sum.  RPL bounds rank by 32 * RPL.
+constexpr int kHeadsPerBlock = 4;
+
+template <typename T, int RPL>
+__global__ void __launch_bounds__(128)
+latent_attention_kernel(const float* __restrict__ wide, int64_t ldw, const T* __restrict__ cache, const int32_t* __restrict__ tok_seq,
+                        const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
+                        int64_t ldo, int n_head, int rank, int rot, int page_size, float scale, int window) {
+    extern __shared__ float sm[];
+    const int D = rank + rot, DS = D | 1;                 // odd row stride: lanes reading one column of 32 rows hit 32 banks
+    float* qs = sm;                                        // [4][D]
+    float* tile = qs + kHeadsPerBlock * D;                 // [32][DS]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * kHeadsPerBlock + warp;
+    const bool active = h < n_head;
+    const int p = positions[t];
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
+    for (int i = threadIdx.x; i < kHeadsPerBlock * D; i += blockDim.x) {
+        const int hh = blockIdx.y * kHeadsPerBlock + i / D;
+        qs[i] = hh < n_head ? wide[(size_t)t * ldw + (size_t)hh * D + (i % D)] : 0.0f;
+    }
+    float m = -CUDART_INF_F, l = 0.0f, o[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) o[r] = 0.0f;
+    const float* qh = qs + warp * D;
+    for (int j0 = lo; j0 <= p; j0 += 32) {
+        __syncthreads();                                   // the tile of the step before has been used (and qs is written)
+        for (int kk = warp; kk < 32; kk += 4) {
+            const int j = j0 + kk;
+            float* dst = tile + kk * DS;
+            if (j <= p) {
+                const T* src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D;
+                for (int d = lane; d < D; d += 32) dst[d] = lb_to_float(src[d]);
+            } else {
+                for (int d = lane; d < D; d += 32) dst[d] = 0.0f;
+            }
+        }
+        __syncthreads();
+        if (!active) continue;
+        const float* row = tile + lane * DS;
+        float dot = 0.0f;
+        for (int d = 0; d < D; ++d) dot = fmaf(qh[d], row[d], dot);
+        const float sc = j0 + lane <= p ? dot * scale : -CUDART_INF_F;
+        const float m_new = fmaxf(m, lb_warp_max(sc));     // finite: the step's first row is visible
+        const float corr = expf(m - m_new);               // 0 at the first step (m = -inf)
+        const float pj = expf(sc - m_new);
+        l = l * corr + lb_warp_sum(pj);
+#pragma unroll
+        for (int r = 0; r < RPL; ++r) o[r] *= corr;
+        for (int kk = 0; kk < 32; ++kk) {
+            const float pk = __shfl_sync(0xffffffffu, pj, kk);
+            const float* c = tile + kk * DS;
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) {
+                const int d = lane + 32 * r;
+                if (d < rank) o[r] = fmaf(pk, c[d], o[r]);
+            }
+        }
+        m = m_new;
+    }
+    if (!active) return;
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int d = lane + 32 * r;
+        if (d < rank) out[(size_t)t * ldo + (size_t)h * rank + d] = o[r] * inv;
+    }
+}
+
+template <typename T, int RPL>
+int launch_latent_attention(const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                            const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens, int n_head, int rank, int rot,
+                            int page_size, float scale, int window, cudaStream_t s) {
+    const int D = rank + rot;
+    const size_t smem = ((size_t)kHeadsPerBlock * D + 32 * (size_t)(D | 1)) * sizeof(float);
+    if (smem > 220 * 1024) return lb_fail(LB_ERR_UNSUPPORTED, "latent attention: cache rows of %d values do not fit a block", D);
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<T, RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid(n_tokens, (n_head + kHeadsPerBlock - 1) / kHeadsPerBlock);
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_kernel<T, RPL>, grid, dim3(128), smem, s, wide, ldw, (const T*)cache, tok_seq, positions,
+                                       block_table, table_stride, out, ldo, n_head, rank, rot, page_size, scale, window));
+    return LB_OK;
+}
+
+template <typename T>
+int pick_latent_attention(const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                          const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens, int n_head, int rank, int rot,
+                          int page_size, float scale, int window, cudaStream_t s) {
+#define LB_LATENT(RPL) launch_latent_attention<T, RPL>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, \
+                                                       rank, rot, page_size, scale, window, s)
+    if (rank <= 128) return LB_LATENT(4);
+    if (rank <= 256) return LB_LATENT(8);
+    if (rank <= 512) return LB_LATENT(16);
+    if (rank <= 1024) return LB_LATENT(32);
+#undef LB_LATENT
+    return lb_fail(LB_ERR_UNSUPPORTED, "latent attention: a latent of %d values is more than the kernel takes (1024)", rank);
+}
+
+template <typename TA, typename TB, typename TC>
+int launch_head_matmul(const void* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
+                       int64_t c_head, int M, int N, int K, int n_head, cudaStream_t s) {
+    const dim3 grid((N + 63) / 64, (M + 31) / 32, n_head);
+    LB_CHECK_CUDA(lb_launch_overlapped(head_matmul_kernel<TA, TB, TC>, grid, dim3(256), 0, s, (const TA*)A, lda, a_head, (const TB*)B, b_head, b_k, b_n,
+                                       (TC*)C, ldc, c_head, M, N, K));
+    return LB_OK;
+}
+
+}  // namespace
+
+extern "C" int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
+                               const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && rank > 0 && rot >= 0 && rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0,
+                 "latent store: bad sizes rank=%d rot=%d rotated=%d", rank, rot, rot_dims);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int threads = rank >= 512 ? 256 : 128;
+    if (cache_dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(latent_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, d, ldd, gain, freq, positions, slot_mapping,
+                                           (float*)cache, rank, rot, rot_dims, eps));
+    else if (cache_dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(latent_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, d, ldd, gain, freq, positions,
+                                           slot_mapping, (__nv_bfloat16*)cache, rank, rot, rot_dims, eps));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "latent store: unknown dtype %d", cache_dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_rope_heads(int q_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, float* wide, int64_t ldw,
+                             int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && dim >= 0 && rot >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rank > 0,
+                 "rotation of queries: bad sizes heads=%d dim=%d rot=%d rotated=%d", n_head, dim, rot, rot_dims);
+    if (n_tokens == 0 || rot == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (q_dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions, wide, ldw,
+                                           n_head, dim, rot, rot_dims, rank));
+    else if (q_dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, (const __nv_bfloat16*)q, ldq, freq,
+                                           positions, wide, ldw, n_head, dim, rot, rot_dims, rank));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "rotation of queries: unknown dtype %d", q_dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_head_matmul(int a_dtype, int b_dtype, int c_dtype, const void* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head,
+                              int64_t b_k, int64_t b_n, void* C, int64_t ldc, int64_t c_head, int M, int N, int K, int n_head, void* stream) {
+    LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && n_head > 0 && n_head <= 65535, "product per head: bad sizes M=%d N=%d K=%d heads=%d", M, N, K, n_head);
+    if (M == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    using B16 = __nv_bfloat16;
+#define LB_HEADS(TA, TB, TC) return launch_head_matmul<TA, TB, TC>(A, lda, a_head, B, b_head, b_k, b_n, C, ldc, c_head, M, N, K, n_head, s)
+    if (a_dtype == LB_F32 && b_dtype == LB_F32 && c_dtype == LB_F32) LB_HEADS(float, float, float);
+    if (a_dtype == LB_BF16 && b_dtype == LB_BF16 && c_dtype == LB_F32) LB_HEADS(B16, B16, float);
+    if (a_dtype == LB_F32 && b_dtype == LB_BF16 && c_dtype == LB_BF16) LB_HEADS(float, B16, B16);
+    if (a_dtype == LB_F32 && b_dtype == LB_BF16 && c_dtype == LB_F32) LB_HEADS(float, B16, float);
+#undef LB_HEADS
+    return lb_fail(LB_ERR_UNSUPPORTED, "product per head: element types %d x %d -> %d are not built", a_dtype, b_dtype, c_dtype);
+}
+
+extern "C" int lb_latent_attention(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
+                                   const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
+                                   int n_head, int rank, int rot, int page_size, float scale, int window, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && rank > 0 && rot >= 0 && page_size > 0 && window >= 0,
+                 "latent attention: bad sizes heads=%d rank=%d rot=%d page=%d window=%d", n_head, rank, rot, page_size, window);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (cache_dtype == LB_F32)
+        return pick_latent_attention<float>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, rank, rot,
+                                            page_size, scale, window, s);
+    if (cache_dtype == LB_BF16)
+        return pick_latent_attention<__nv_bfloat16>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, rank,
+                                                    rot, page_size, scale, window, s);
+    return lb_fail(LB_ERR_INVALID_ARGUMENT, "latent attention: unknown dtype %d", cache_dtype);
+}

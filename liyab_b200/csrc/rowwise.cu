@@ -1,0 +1,298 @@
+// Row-wise pieces that sit between the matrix products of a block: the RMS norm in groups, the blend of a
+// token's normalised row with the row before it (token shift, with the last row of every request kept as state),
+// the xIELU activation, and the gated per-token side input.  Statistics, blends and activations are 32-bit
+// whatever the element type of the rows.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- RMS norm in groups
+// The row is cut into `groups` equal consecutive parts; y = x / sqrt(mean(part^2) + eps) * w.  One block per
+// (row, group); the sum's order depends on the part's length alone.
+template <typename T>
+__global__ void rms_groups_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows, const float* __restrict__ w,
+                                  T* __restrict__ y, int64_t ldy, int part, float eps) {
+    __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int r = blockIdx.x, g = blockIdx.y;
+    const float* in = x + (size_t)(rows != nullptr ? rows[r] : r) * ldx + (size_t)g * part;
+    const float* gain = w != nullptr ? w + (size_t)g * part : nullptr;
+    T* out = y + (size_t)r * ldy + (size_t)g * part;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = in[i] * inv;
+        if (gain != nullptr) v *= gain[i];
+        out[i] = lb_from_float<T>(v);
+    }
+}
+
+// ---------------------------------------------------------------- the same norm and the token shift in one pass
+// Block t makes h_t = norm(x_t) (written to `h`) and the mixer's input m_t = h_t + (prev - h_t) * mu, where prev is
+// the norm of row t - 1 (made again here, so no block waits for another) or, for the first row of a request's
+// portion, the request's state.  Both h_t and prev pass through the element type T first, so that a row blends
+// with the same numbers whether its neighbour came in this step or in an earlier one.
+template <typename T>
+__global__ void rms_shift_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ mu,
+                                 T* __restrict__ h, int64_t ldh, T* __restrict__ m, int64_t ldm, T* __restrict__ state,
+                                 const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots,
+                                 int width, int groups, float eps) {
+    extern __shared__ float inv_of[];          // [2][groups]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, s = tok_seq[t], first = q_start[s], last = q_start[s + 1] - 1;
+    const int part = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const float* cur = x + (size_t)t * ldx;
+    const float* before = t > first ? x + (size_t)(t - 1) * ldx : nullptr;
+    // A warp per (row, group) sum: lanes stride over the part, then a shuffle tree; order fixed by the part's length.
+    for (int job = warp; job < 2 * groups; job += n_warps) {
+        const float* row = job < groups ? cur : before;
+        if (row == nullptr) continue;
+        const float* in = row + (size_t)(job % groups) * part;
+        float ss = 0.0f;
+        for (int i = lane; i < part; i += 32) ss = fmaf(in[i], in[i], ss);
+        ss = lb_warp_sum(ss);
+        if (lane == 0) inv_of[job] = 1.0f / sqrtf(ss / (float)part + eps);
+    }
+    __syncthreads();
+    T* keep = state + (size_t)slots[s] * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const int g = i / part;
+        const T hc = lb_from_float<T>(cur[i] * inv_of[g] * w[i]);
+        const T hp = before != nullptr ? lb_from_float<T>(before[i] * inv_of[groups + g] * w[i]) : keep[i];
+        const float c = lb_to_float(hc), p = lb_to_float(hp);
+        h[(size_t)t * ldh + i] = hc;
+        m[(size_t)t * ldm + i] = lb_from_float<T>(c + (p - c) * mu[i]);
+        if (first == last) keep[i] = hc;       // a single token: this block read the state and may replace it
+    }
+}
+
+// The token shift alone, from rows that are already normalised.
+template <typename T>
+__global__ void shift_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ mu, T* __restrict__ m, int64_t ldm,
+                             T* __restrict__ state, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ q_start,
+                             const int32_t* __restrict__ slots, int width) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, s = tok_seq[t], first = q_start[s], last = q_start[s + 1] - 1;
+    T* keep = state + (size_t)slots[s] * width;
+    const T* prev = t > first ? h + (size_t)(t - 1) * ldh : keep;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const T hc = h[(size_t)t * ldh + i];
+        const float c = lb_to_float(hc), p = lb_to_float(prev[i]);
+        m[(size_t)t * ldm + i] = lb_from_float<T>(c + (p - c) * mu[i]);
+        if (first == last) keep[i] = hc;
+    }
+}
+
+// The state of requests that brought more than one token: their last normalised row.  Runs after the shift, whose
+// first-row blocks read the state.
+template <typename T>
+__global__ void shift_keep_kernel(const T* __restrict__ h, int64_t ldh, T* __restrict__ state, const int32_t* __restrict__ q_start,
+                                  const int32_t* __restrict__ slots, int width) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int s = blockIdx.x, first = q_start[s], last = q_start[s + 1] - 1;
+    if (last <= first) return;
+    T* keep = state + (size_t)slots[s] * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) keep[i] = h[(size_t)last * ldh + i];
+}
+
+// ---------------------------------------------------------------- xIELU
+// z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2, with a = softplus(p) and b = 1/2 + softplus(q).
+__device__ __forceinline__ float softplus(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
+
+template <typename T>
+__global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int cols, const float* __restrict__ pq) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const float a = softplus(pq[0]), b = 0.5f + softplus(pq[1]);
+    T* row = z + (size_t)blockIdx.x * ldz;
+    for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) {
+        const float v = lb_to_float(row[i]);
+        const float r = v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v);
+        row[i] = lb_from_float<T>(r);
+    }
+}
+
+// ---------------------------------------------------------------- gated per-token side input
+// For NT consecutive tokens a block makes g = gelu_tanh(G x) * e (e: the token's row of the side table), y = P g
+// and x += y / sqrt(mean(y^2) + eps) * w.  G is [dim, width], P is [width, dim]; the rows of x are 32-bit and stay so.
+// The weights are read once per block, whatever NT.
+template <typename T, int NT>
+__global__ void __launch_bounds__(256)
+token_side_kernel(float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ tokens, const T* __restrict__ table, const T* __restrict__ G,
+                  const T* __restrict__ P, const float* __restrict__ w, int n_tokens, int width, int dim, float eps) {
+    extern __shared__ float sm[];              // x rows [NT][width], then y rows [NT][width], then g [NT][dim], then sums
+    float* xs = sm;
+    float* ys = xs + (size_t)NT * width;
+    float* gs = ys + (size_t)NT * width;
+    float* red = gs + (size_t)NT * dim;        // [NT][8 warps] + [NT]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t0 = blockIdx.x * NT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nt = min(NT, n_tokens - t0);
+    for (int i = threadIdx.x; i < NT * width; i += blockDim.x) {
+        const int u = i / width, c = i - u * width;
+        xs[i] = u < nt ? x[(size_t)(t0 + u) * ldx + c] : 0.0f;
+    }
+    __syncthreads();
+    // g: a warp per gate feature, lanes along the width.
+    for (int d = warp; d < dim; d += 8) {
+        const T* row = G + (size_t)d * width;
+        float acc[NT];
+#pragma unroll
+        for (int u = 0; u < NT; ++u) acc[u] = 0.0f;
+        for (int c = lane; c < width; c += 32) {
+            const float gv = lb_to_float(row[c]);
+#pragma unroll
+            for (int u = 0; u < NT; ++u) acc[u] = fmaf(gv, xs[u * width + c], acc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < NT; ++u) {
+            const float v = lb_warp_sum(acc[u]);
+            if (lane == 0 && u < nt) gs[u * dim + d] = lb_gelu_tanh(v) * lb_to_float(table[(size_t)tokens[t0 + u] * dim + d]);
+        }
+    }
+    __syncthreads();
+    // y: a thread per output column, the short row of P in order.
+    float ss[NT];
+#pragma unroll
+    for (int u = 0; u < NT; ++u) ss[u] = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const T* row = P + (size_t)c * dim;
+        float acc[NT];
+#pragma unroll
+        for (int u = 0; u < NT; ++u) acc[u] = 0.0f;
+        for (int d = 0; d < dim; ++d) {
+            const float pv = lb_to_float(row[d]);
+#pragma unroll
+            for (int u = 0; u < NT; ++u) acc[u] = fmaf(pv, gs[u * dim + d], acc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < NT; ++u) {
+            ys[u * width + c] = acc[u];
+            ss[u] = fmaf(acc[u], acc[u], ss[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+        const float v = lb_warp_sum(ss[u]);
+        if (lane == 0) red[u * 8 + warp] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < NT) {
+        float total = 0.0f;
+        for (int k = 0; k < 8; ++k) total += red[threadIdx.x * 8 + k];
+        red[NT * 8 + threadIdx.x] = 1.0f / sqrtf(total / (float)width + eps);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * width; i += blockDim.x) {
+        const int u = i / width, c = i - u * width;
+        x[(size_t)(t0 + u) * ldx + c] = xs[i] + ys[i] * red[NT * 8 + u] * w[c];
+    }
+}
+
+template <typename T, int NT>
+int launch_token_side(float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* G, const void* P, const float* w,
+                      int n_tokens, int width, int dim, float eps, cudaStream_t s) {
+    const size_t smem = ((size_t)NT * (2 * width + dim) + NT * 9) * sizeof(float);
+    if (smem > 200 * 1024) return lb_fail(LB_ERR_UNSUPPORTED, "token side input: rows of %d values with %d gate features do not fit a block", width, dim);
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(token_side_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LB_CHECK_CUDA(lb_launch_overlapped(token_side_kernel<T, NT>, dim3((n_tokens + NT - 1) / NT), dim3(256), smem, s, x, ldx, tokens,
+                                       (const T*)table, (const T*)G, (const T*)P, w, n_tokens, width, dim, eps));
+    return LB_OK;
+}
+
+}  // namespace
+
+extern "C" int lb_rms_groups(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, void* y, int64_t ldy,
+                             int n_rows, int width, int groups, float eps, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && width > 0 && groups > 0 && width % groups == 0, "rms norm: %d values do not split into %d equal groups", width, groups);
+    if (n_rows == 0) return LB_OK;
+    const int part = width / groups, threads = part >= 1024 ? 256 : part >= 256 ? 128 : part > 32 ? 64 : 32;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (out_dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(rms_groups_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, x, ldx, rows, weight, (float*)y, ldy, part, eps));
+    else if (out_dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(rms_groups_kernel<__nv_bfloat16>, dim3(n_rows, groups), dim3(threads), 0, s, x, ldx, rows, weight,
+                                           (__nv_bfloat16*)y, ldy, part, eps));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "rms norm: unknown dtype %d", out_dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_rms_shift(int dtype, const float* x, int64_t ldx, const float* weight, const float* mix, void* h, int64_t ldh, void* m,
+                            int64_t ldm, void* state, const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, int n_tokens,
+                            int n_seq, int decode_only, int width, int groups, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0 && groups > 0 && width % groups == 0, "rms norm: %d values do not split into %d equal groups", width, groups);
+    LB_CHECK_ARG(groups <= 4096, "rms norm: %d groups are more than a block keeps", groups);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int threads = width >= 1024 ? 256 : 128;
+    const size_t smem = 2 * (size_t)groups * sizeof(float);
+    if (dtype == LB_F32) {
+        LB_CHECK_CUDA(lb_launch_overlapped(rms_shift_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, x, ldx, weight, mix, (float*)h, ldh, (float*)m,
+                                           ldm, (float*)state, tok_seq, q_start, slots, width, groups, eps));
+        if (!decode_only)
+            LB_CHECK_CUDA(lb_launch_overlapped(shift_keep_kernel<float>, dim3(n_seq), dim3(threads), 0, s, (const float*)h, ldh, (float*)state, q_start, slots, width));
+    } else if (dtype == LB_BF16) {
+        using B = __nv_bfloat16;
+        LB_CHECK_CUDA(lb_launch_overlapped(rms_shift_kernel<B>, dim3(n_tokens), dim3(threads), smem, s, x, ldx, weight, mix, (B*)h, ldh, (B*)m, ldm,
+                                           (B*)state, tok_seq, q_start, slots, width, groups, eps));
+        if (!decode_only)
+            LB_CHECK_CUDA(lb_launch_overlapped(shift_keep_kernel<B>, dim3(n_seq), dim3(threads), 0, s, (const B*)h, ldh, (B*)state, q_start, slots, width));
+    } else return lb_fail(LB_ERR_INVALID_ARGUMENT, "token shift: unknown dtype %d", dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_token_shift(int dtype, const void* h, int64_t ldh, const float* mix, void* m, int64_t ldm, void* state,
+                              const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, int n_tokens, int n_seq, int decode_only,
+                              int width, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0, "token shift: bad sizes n_tokens=%d width=%d", n_tokens, width);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == LB_F32) {
+        LB_CHECK_CUDA(lb_launch_overlapped(shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)h, ldh, mix, (float*)m, ldm, (float*)state,
+                                           tok_seq, q_start, slots, width));
+        if (!decode_only)
+            LB_CHECK_CUDA(lb_launch_overlapped(shift_keep_kernel<float>, dim3(n_seq), dim3(threads), 0, s, (const float*)h, ldh, (float*)state, q_start, slots, width));
+    } else if (dtype == LB_BF16) {
+        using B = __nv_bfloat16;
+        LB_CHECK_CUDA(lb_launch_overlapped(shift_kernel<B>, dim3(n_tokens), dim3(threads), 0, s, (const B*)h, ldh, mix, (B*)m, ldm, (B*)state, tok_seq,
+                                           q_start, slots, width));
+        if (!decode_only)
+            LB_CHECK_CUDA(lb_launch_overlapped(shift_keep_kernel<B>, dim3(n_seq), dim3(threads), 0, s, (const B*)h, ldh, (B*)state, q_start, slots, width));
+    } else return lb_fail(LB_ERR_INVALID_ARGUMENT, "token shift: unknown dtype %d", dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_xielu(int dtype, void* z, int64_t ldz, int n_rows, int cols, const float* pq, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && cols > 0 && pq != nullptr, "xielu: bad sizes n_rows=%d cols=%d", n_rows, cols);
+    if (n_rows == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const dim3 grid(n_rows, (cols + 2047) / 2048);
+    if (dtype == LB_F32) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
+    else if (dtype == LB_BF16) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "xielu: unknown dtype %d", dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_token_side(int dtype, float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* gate, const void* proj,
+                             const float* weight, int n_tokens, int width, int dim, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0 && dim > 0, "token side input: bad sizes n_tokens=%d width=%d dim=%d", n_tokens, width, dim);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    // Few tokens: a block each, so that the step spreads over the GPU; many: eight a block share one pass over the weights.
+    const bool many = n_tokens > 64 && ((size_t)8 * (2 * width + dim) + 72) * sizeof(float) <= 200 * 1024;
+    if (dtype == LB_F32)
+        return many ? launch_token_side<float, 8>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s)
+                    : launch_token_side<float, 1>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s);
+    if (dtype == LB_BF16)
+        return many ? launch_token_side<__nv_bfloat16, 8>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s)
+                    : launch_token_side<__nv_bfloat16, 1>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s);
+    return lb_fail(LB_ERR_INVALID_ARGUMENT, "token side input: unknown dtype %d", dtype);
+}

@@ -54,6 +54,7 @@ private:
 }  // namespace
 
 void register_gpt2();      // gpt2.cpp
+void register_puzutar();   // puzutar.cpp
 
 void register_architecture(Architecture arch) { table()[arch.name] = std::move(arch); }
 
@@ -61,6 +62,7 @@ void register_builtin_architectures() {
     static std::once_flag once;
     std::call_once(once, [] {
         register_gpt2();
+        register_puzutar();
         register_architecture({"liyab_spec", {}, [](const Json& raw) { return std::make_unique<SpecConfig>(raw); }});
     });
     // Plug-ins named by the environment (paths separated by ':') are loaded once, so that the programs can run
@@ -90,8 +92,14 @@ const Architecture& find_architecture(const Json& config) {
     register_builtin_architectures();
     if (!config.is_object()) throw invalid_model("config.json does not hold a JSON object");
     const Json* name = config.find("model_type");
+    if (name == nullptr || !name->is_string()) name = config.find("architecture");      // some designs name themselves so
     if (name != nullptr && name->is_string()) {
-        const auto it = table().find(name->as_string());
+        auto it = table().find(name->as_string());
+        if (it == table().end()) {             // rows are registered in lower case
+            std::string lower = name->as_string();
+            std::transform(lower.begin(), lower.end(), lower.begin(), [](unsigned char c) { return static_cast<char>(std::tolower(c)); });
+            it = table().find(lower);
+        }
         if (it != table().end()) return it->second;
     }
     std::string shown = name != nullptr && name->is_string() ? name->as_string() : "";

@@ -1,4 +1,5 @@
 #include "builtin_parts.h"
+#include "parallel_parts.h"
 
 #include <mutex>
 
@@ -23,6 +24,21 @@ void register_builtin_parts() {
         feed_forwards().add("dense", {DenseFeedForward::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
                                           return std::make_shared<DenseFeedForward>(s, p);
                                       }});
+        norms().add("rms_norm", {GroupedRmsNorm::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                     return std::make_shared<GroupedRmsNorm>(s, p);
+                                 }});
+        shifts().add("lerp_previous", {LerpShift::parameters, [](const PartSpec& s, const Params& p, const Runtime& rt) {
+                                           return std::make_shared<LerpShift>(s, p, rt);
+                                       }});
+        mixers().add("latent_attention", {LatentAttention::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                              return std::make_shared<LatentAttention>(s, p);
+                                          }});
+        token_inputs().add("gated_side", {GatedTokenSide::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                              return std::make_shared<GatedTokenSide>(s, p);
+                                          }});
+        arrangements().add("parallel", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
+                               return std::make_shared<ParallelBlock>(l, parts);
+                           }});
         arrangements().add("pre_norm", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
                                return std::make_shared<PreNormBlock>(l, parts);
                            }});

@@ -239,6 +239,8 @@ public:
 };
 
 // ---- the dense, ungated feed-forward: down(act(up(x))) ----------------------------------------------
+// Activations: gelu_tanh, gelu_erf, none (in the first product's epilogue) and xielu (z > 0: softplus(p) z^2 + z/2; else
+// (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with the learned pair `act` = (p, q)).
 // Reference: dense_ffn, ungated branch (src/core/transformer.cpp:4903-4913) with the activations of :125-142.
 // Bias and activation ride in the first product's epilogue, bias and the residual sum in the second's.
 
@@ -246,7 +248,10 @@ class DenseFeedForward final : public FeedForward {
 public:
     DenseFeedForward(const PartSpec& s, const Params& p) {
         inner = need_int(s, "inner");
-        activation = kernels::activation_from_name(s.options.get_string("activation", "gelu_tanh"));
+        const std::string act = s.options.get_string("activation", "gelu_tanh");
+        // The xIELU has two learned numbers of its own and runs as a kernel between the two products.
+        if (act == "xielu") xielu = f32_or_null(&p.at("act"));
+        activation = act == "xielu" ? kernels::kNone : kernels::activation_from_name(act);
         up = Linear(p, "up.", "feed_forward.up");
         down = Linear(p, "down.", "feed_forward.down");
     }
@@ -256,6 +261,7 @@ public:
         std::vector<ParamDecl> out;
         Linear::declare(out, "up.", inner, hidden, bias);
         Linear::declare(out, "down.", hidden, inner, bias);
+        if (s.options.get_string("activation", "gelu_tanh") == "xielu") out.push_back({"act", {2}, ParamKind::Vector});
         return out;
     }
     bool capturable() const override { return true; }
@@ -263,12 +269,13 @@ public:
         const int T = ctx.n_tokens;
         const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
         up.forward(ctx, h, mid, T, activation);
+        if (xielu != nullptr) kernels::xielu(ctx.stream(), mid, T, xielu);
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
     }
     // As the attention's: the up projection of a few tokens normalises the rows inside its kernel.
     bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) override {
         const int T = ctx.n_tokens;
-        if (!kernels::gemm_rows_normed_supports(ctx.runtime, x_in, up.weight, T)) return false;
+        if (xielu != nullptr || !kernels::gemm_rows_normed_supports(ctx.runtime, x_in, up.weight, T)) return false;
         const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
         kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, up.weight, up.bias, mid, T, activation, nullptr, nullptr);
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
@@ -276,6 +283,7 @@ public:
     }
     int64_t inner = 0;
     int activation = 0;
+    const float* xielu = nullptr;      // the activation's two learned numbers (p, q), where it is the xIELU
     Linear up, down;
 };
 

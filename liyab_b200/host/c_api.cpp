@@ -854,8 +854,9 @@ int32_t lb_trace_run_main(int32_t argc, const char* const* argv) {
     std::string model, dtype, out_dir;
     int64_t max_tokens = 0;
     ReplayerOptions options;
+    options.max_requests = 4;       // state slots and table rows for this many live requests; finished requests' are used again
     auto usage = [] {
-        std::fprintf(stderr, "usage: trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--device D] [--page-size 16|32|64]\n"
+        std::fprintf(stderr, "usage: trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--device D] [--page-size 16|32|64] [--max-requests 4]\n"
                              "Replays given token ids through the engine (steps as JSON lines on standard input) and writes logits.\n");
     };
     for (int i = 1; i < argc; ++i) {
@@ -871,6 +872,7 @@ int32_t lb_trace_run_main(int32_t argc, const char* const* argv) {
             else if (a == "--max-tokens") max_tokens = std::stoll(value());
             else if (a == "--device") { std::string d = value(); if (d.rfind("cuda:", 0) == 0) d = d.substr(5); options.device = std::stoi(d); }
             else if (a == "--page-size") options.page_size = std::stoi(value());
+            else if (a == "--max-requests") options.max_requests = std::stoi(value());
             else if (a == "-h" || a == "--help") { usage(); return 0; }
             else { usage(); std::fprintf(stderr, "trace_run: unknown option %s\n", a.c_str()); return 2; }
         } catch (const std::exception& e) {
@@ -879,7 +881,7 @@ int32_t lb_trace_run_main(int32_t argc, const char* const* argv) {
         }
     }
     if (model.empty() || dtype.empty() || out_dir.empty() || max_tokens <= 0 || (dtype != "bfloat16" && dtype != "float32") ||
-        (options.page_size != 16 && options.page_size != 32 && options.page_size != 64)) {
+        (options.page_size != 16 && options.page_size != 32 && options.page_size != 64) || options.max_requests < 1) {
         usage();
         return 2;
     }

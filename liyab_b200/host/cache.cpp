@@ -56,7 +56,7 @@ int KvGroup::unit_index(int unit) const {
 }
 
 size_t KvGroup::unit_bytes() const {
-    return static_cast<size_t>(pool.num_pages()) * 2 * static_cast<size_t>(need.n_kv_head) * static_cast<size_t>(page_size) *
+    return static_cast<size_t>(pool.num_pages()) * static_cast<size_t>(need.planes) * static_cast<size_t>(need.n_kv_head) * static_cast<size_t>(page_size) *
            static_cast<size_t>(need.head_dim) * dtype_size(storage_dtype);
 }
 
@@ -66,7 +66,7 @@ void* KvGroup::unit_storage(int unit) const {
 }
 
 size_t KvGroup::bytes_per_token(size_t element_size) const {
-    return 2 * units.size() * static_cast<size_t>(need.n_kv_head) * static_cast<size_t>(need.head_dim) * element_size;
+    return static_cast<size_t>(need.planes) * units.size() * static_cast<size_t>(need.n_kv_head) * static_cast<size_t>(need.head_dim) * element_size;
 }
 
 int64_t KvGroup::pages_needed(int row, int64_t end) const {

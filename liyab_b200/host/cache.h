@@ -4,7 +4,7 @@
 // What it owns.  Cache *units* (one per entry of the run order that writes keys
 // and values) are sorted into *groups* by what they need: number of key/value
 // heads, head size and attention window.  Each group has pages of its own (one
-// device array [unit, page, K|V, kv_head, slot, head_dim] and one free list) and
+// device array [unit, page, plane (K|V, or one), kv_head, slot, head_dim] and one free list) and
 // one block table per request, shared by the group's units, so a page id means the
 // same positions in every unit of the group.  Pages return to the free list when a
 // request closes, when it is cut back, and, in a windowed group, as soon as no
@@ -47,6 +47,7 @@ struct KvNeed {
     int n_kv_head = 0;
     int head_dim = 0;
     int window = 0;          // 0: every position is kept; w: the w latest positions
+    int planes = 2;          // rows kept per position and head: 2 (a key and a value) or 1 (one row that serves as both)
     auto operator<=>(const KvNeed&) const = default;
 };
 

@@ -16,6 +16,8 @@ std::vector<ParamDecl> slot_parameters(const SlotSpec& s) {
         case Role::Norm: return norms().get(s.part.kind).parameters(s.part);
         case Role::Mixer: return mixers().get(s.part.kind).parameters(s.part);
         case Role::FeedForward: return feed_forwards().get(s.part.kind).parameters(s.part);
+        case Role::Shift: return shifts().get(s.part.kind).parameters(s.part);
+        case Role::TokenInput: return token_inputs().get(s.part.kind).parameters(s.part);
     }
     return {};
 }
@@ -25,6 +27,8 @@ std::shared_ptr<Part> build_slot(const SlotSpec& s, const Params& p, const Runti
         case Role::Norm: return norms().get(s.part.kind).build(s.part, p, rt);
         case Role::Mixer: return mixers().get(s.part.kind).build(s.part, p, rt);
         case Role::FeedForward: return feed_forwards().get(s.part.kind).build(s.part, p, rt);
+        case Role::Shift: return shifts().get(s.part.kind).build(s.part, p, rt);
+        case Role::TokenInput: return token_inputs().get(s.part.kind).build(s.part, p, rt);
     }
     return nullptr;
 }
@@ -102,8 +106,11 @@ std::map<int, KvNeed> DecoderModel::kv_needs() const {
         Mixer* m = mixer_of(e);
         const auto mine = m != nullptr ? m->kv_need() : std::nullopt;
         const auto it = out.find(e.cache);
-        if (mine && (it == out.end() || !(it->second == *mine)))
-            throw invalid_model("run order entry {} reads the cache of entry {}, whose keys and values have another shape or window", i, e.cache);
+        if (!mine) continue;
+        // A reader may look further back than the writer (or less far): the unit keeps what the widest of them sees.
+        if (it == out.end() || it->second.n_kv_head != mine->n_kv_head || it->second.head_dim != mine->head_dim || it->second.planes != mine->planes)
+            throw invalid_model("run order entry {} reads the cache of entry {}, whose rows have another shape", i, e.cache);
+        it->second.window = it->second.window == 0 || mine->window == 0 ? 0 : std::max(it->second.window, mine->window);
     }
     return out;
 }
@@ -114,6 +121,10 @@ std::map<int, StateNeed> DecoderModel::state_needs() const {
         Mixer* m = mixer_of(spec.run_order[i]);
         if (m == nullptr) continue;
         if (const auto need = m->state_need()) out[static_cast<int>(i)] = *need;
+    }
+    for (size_t i = 0; i < spec.run_order.size(); ++i) {
+        const auto extra = layers[static_cast<size_t>(spec.run_order[i].layer)].block->extra_states();
+        for (size_t k = 0; k < extra.size(); ++k) out[CacheUnit{0, false, static_cast<int>(i)}.extra_state(static_cast<int>(k))] = extra[k];
     }
     return out;
 }
@@ -145,7 +156,7 @@ Rows DecoderModel::forward(StepContext& ctx) {
     ctx.tap("embed", x);
     for (size_t i = 0; i < spec.run_order.size(); ++i) {
         const RunEntry& e = spec.run_order[i];
-        layers[static_cast<size_t>(e.layer)].block->forward(ctx, x, CacheUnit{e.cache, e.cache == static_cast<int>(i)});
+        layers[static_cast<size_t>(e.layer)].block->forward(ctx, x, CacheUnit{e.cache, e.cache == static_cast<int>(i), static_cast<int>(i)});
     }
     const int R = ctx.n_logit_rows;
     if (R == 0) return Rows{nullptr, DType::F32, 0, spec.vocab_size(), spec.vocab_size()};

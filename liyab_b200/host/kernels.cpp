@@ -270,6 +270,68 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
               "prefill_attention");
 }
 
+void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps) {
+    if (x.dtype != DType::F32 || out.cols != x.cols || out.rows < n_rows) throw invalid_argument("rms norm: buffers must be [rows, width], the input float32");
+    check(lb_rms_groups(code(out.dtype, "out"), x.f32(), x.stride, rows, weight, out.data, out.stride, n_rows, static_cast<int>(x.cols), groups, eps, s),
+          "rms_groups");
+}
+
+void token_shift(cudaStream_t s, const Rows& h, const float* mix, const Rows& m, void* state, const ShiftLayout& l) {
+    if (h.dtype != m.dtype || h.cols != m.cols) throw invalid_argument("token shift: input and output differ in type or width");
+    check(lb_token_shift(code(h.dtype, "h"), h.data, h.stride, mix, m.data, m.stride, state, l.tok_seq, l.q_start, l.slots, l.n_tokens, l.n_seq,
+                         l.decode_only ? 1 : 0, static_cast<int>(h.cols), s), "token_shift");
+    if (!l.decode_only) launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+void rms_shift(cudaStream_t s, const Rows& x, const float* weight, const float* mix, const Rows& h, const Rows& m, void* state,
+               const ShiftLayout& l, int groups, float eps) {
+    if (x.dtype != DType::F32 || h.dtype != m.dtype || h.cols != x.cols || m.cols != x.cols) throw invalid_argument("rms norm with token shift: buffers do not fit");
+    check(lb_rms_shift(code(h.dtype, "h"), x.f32(), x.stride, weight, mix, h.data, h.stride, m.data, m.stride, state, l.tok_seq, l.q_start, l.slots,
+                       l.n_tokens, l.n_seq, l.decode_only ? 1 : 0, static_cast<int>(x.cols), groups, eps, s), "rms_shift");
+    if (!l.decode_only) launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+void xielu(cudaStream_t s, const Rows& z, int n_rows, const float* pq) {
+    check(lb_xielu(code(z.dtype, "z"), z.data, z.stride, n_rows, static_cast<int>(z.cols), pq, s), "xielu");
+}
+
+void token_side(cudaStream_t s, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
+                const float* weight, int n_tokens, float eps) {
+    const int64_t dim = gate.dim(0), width = gate.dim(1);
+    if (x.dtype != DType::F32 || x.cols != width || proj.dim(0) != width || proj.dim(1) != dim || table.dim(1) != dim || gate.dtype != proj.dtype ||
+        gate.dtype != table.dtype)
+        throw invalid_argument("token side input: tensors do not fit");
+    check(lb_token_side(code(gate.dtype, "gate"), x.f32(), x.stride, tokens, table.data, gate.data, proj.data, weight, n_tokens, static_cast<int>(width),
+                        static_cast<int>(dim), eps, s), "token_side");
+}
+
+void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float* freq, const int32_t* positions, const int32_t* slot_mapping,
+                  void* cache, DType cache_dtype, int n_tokens, const LatentShape& a, float eps) {
+    if (d.dtype != DType::F32 || d.cols != a.rank + a.rot) throw invalid_argument("latent store: the rows must be float32 [tokens, rank + rot]");
+    check(lb_latent_store(code(cache_dtype, "cache"), d.f32(), d.stride, gain, freq, positions, slot_mapping, cache, n_tokens, a.rank, a.rot, a.rot_dims,
+                          eps, s), "latent_store");
+}
+
+void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t* positions, const Rows& wide, int n_tokens, const LatentShape& a) {
+    if (wide.dtype != DType::F32 || wide.cols != static_cast<int64_t>(a.n_head) * (a.rank + a.rot) || q.cols != static_cast<int64_t>(a.n_head) * (a.dim + a.rot))
+        throw invalid_argument("rotation of queries: buffers do not fit");
+    check(lb_rope_heads(code(q.dtype, "q"), q.data, q.stride, freq, positions, wide.f32(), wide.stride, n_tokens, a.n_head, a.dim, a.rot, a.rot_dims,
+                        a.rank, s), "rope_heads");
+}
+
+void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
+                 int64_t c_head, int m, int n, int k, int n_head) {
+    check(lb_head_matmul(code(a.dtype, "a"), code(b.dtype, "b"), code(c.dtype, "c"), a.data, a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride,
+                         c_head, m, n, k, n_head, s), "head_matmul");
+}
+
+void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a) {
+    if (wide.dtype != DType::F32 || out.dtype != DType::F32) throw invalid_argument("latent attention: wide queries and attended latents are float32");
+    check(lb_latent_attention(code(cache_dtype, "cache"), wide.f32(), wide.stride, cache, tok_seq, positions, block_table, table_width, out.f32(),
+                              out.stride, n_tokens, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, s), "latent_attention");
+}
+
 void sample(cudaStream_t s, const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
             const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids) {
     check(lb_sample(logits, row_stride, n_rows, vocab, temperature, top_k, top_p, uniform, out_ids, nullptr, s), "sample");

@@ -97,6 +97,43 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
                        const int32_t* n_past, const int32_t* block_table, int table_width, const Rows& out, int n_seq,
                        int max_q_len, const AttentionShape& a);
 
+// ---- row-wise pieces between the products: RMS norm in groups, token shift, xIELU, gated side input ----
+// out[r] = x[rows ? rows[r] : r] cut into `groups` equal parts, each over its own root mean square, times weight.
+void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps);
+// The step's layout as the shift kernels need it.
+struct ShiftLayout {
+    const int32_t* tok_seq = nullptr;
+    const int32_t* q_start = nullptr;
+    const int32_t* slots = nullptr;
+    int n_tokens = 0, n_seq = 0;
+    bool decode_only = false;
+};
+// m[t] = h[t] + (h[t - 1] - h[t]) * mix, the row before a request's first row taken from (and its last row left in) `state`.
+void token_shift(cudaStream_t s, const Rows& h, const float* mix, const Rows& m, void* state, const ShiftLayout& l);
+// h = rms_groups(x) and m = token_shift(h) in one pass over x.
+void rms_shift(cudaStream_t s, const Rows& x, const float* weight, const float* mix, const Rows& h, const Rows& m, void* state,
+               const ShiftLayout& l, int groups, float eps);
+// In place over z[:n_rows]: the xIELU with its two learned numbers pq (float, on the device).
+void xielu(cudaStream_t s, const Rows& z, int n_rows, const float* pq);
+// x[t] += rms(proj (gelu_tanh(gate x[t]) * table[tokens[t]])) * weight.
+void token_side(cudaStream_t s, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
+                const float* weight, int n_tokens, float eps);
+
+// ---- attention over a cache of latent rows [c (rank) | r (rot)] ----
+struct LatentShape {
+    int n_head = 0, dim = 0, rot = 0, rot_dims = 0, vdim = 0, rank = 0, page_size = 0;
+    float scale = 1.0f;
+    int window = 0;
+};
+void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float* freq, const int32_t* positions, const int32_t* slot_mapping,
+                  void* cache, DType cache_dtype, int n_tokens, const LatentShape& a, float eps);
+void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t* positions, const Rows& wide, int n_tokens, const LatentShape& a);
+// C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n].
+void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
+                 int64_t c_head, int m, int n, int k, int n_head);
+void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a);
+
 void sample(cudaStream_t s, const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
             const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids);
 

@@ -83,6 +83,14 @@ Registry<PartFactory<FeedForward>>& feed_forwards() {
     static Registry<PartFactory<FeedForward>> r("feed-forward");
     return r;
 }
+Registry<PartFactory<Shift>>& shifts() {
+    static Registry<PartFactory<Shift>> r("token shift");
+    return r;
+}
+Registry<PartFactory<TokenInput>>& token_inputs() {
+    static Registry<PartFactory<TokenInput>> r("token input");
+    return r;
+}
 Registry<ArrangementFactory>& arrangements() {
     static Registry<ArrangementFactory> r("block arrangement");
     return r;

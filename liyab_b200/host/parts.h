@@ -53,6 +53,11 @@ private:
 struct CacheUnit {
     int read = 0;
     bool write = true;
+    int entry = 0;           // this run's own place in the run order
+    // Where the k-th extra state of this run's block lives (Arrangement::extra_states); the mixer's own state, if it
+    // keeps one, lives under `read`.
+    static constexpr int kExtraStride = 1 << 20;
+    int extra_state(int k) const { return entry + (k + 1) * kExtraStride; }
 };
 
 // One cache group as a step sees it.
@@ -173,6 +178,24 @@ public:
     virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) { return false; }
 };
 
+// A blend of every row of the mixer's input with the row before it in its sequence.  The last row a request brought
+// is its state; a request's first row blends with zeros (state slots are cleared when a request opens).
+class Shift : public Part {
+public:
+    virtual StateNeed state_need() const = 0;
+    // m[t] = blend(h[t], h[t - 1]) for the step's tokens; `state` is the part's storage [slot, ...].
+    virtual void forward(StepContext& ctx, const Rows& h, const Rows& m, void* state) = 0;
+    // The same with the norm before it, from the float rows x: h = norm(x) and m in one pass.  False (and nothing
+    // done) where the two do not fuse.
+    virtual bool forward_normed(StepContext& ctx, const Rows& x, Norm& norm, const Rows& h, const Rows& m, void* state) { return false; }
+};
+
+// An addition to the residual stream that depends on the step's token ids (and on the stream itself).
+class TokenInput : public Part {
+public:
+    virtual void forward(StepContext& ctx, const Rows& x) = 0;
+};
+
 // The built parts of one layer, by slot name.
 struct LayerParts {
     std::map<std::string, std::shared_ptr<Part>> by_name;
@@ -192,6 +215,9 @@ public:
     virtual void forward(StepContext& ctx, const Rows& x, CacheUnit unit) = 0;
     // The mixers of the layer, for the cache manager's needs (usually one).
     virtual std::vector<Mixer*> mixers() const = 0;
+    // State per request that the block keeps beside its mixer's (a token shift's last row); the k-th entry is
+    // found at ctx.state(unit.extra_state(k)).
+    virtual std::vector<StateNeed> extra_states() const { return {}; }
 };
 
 // -- registries ---------------------------------------------------------------------------------
@@ -236,6 +262,8 @@ Registry<PartFactory<Norm>>& norms();
 Registry<PartFactory<PositionEncoding>>& positions();
 Registry<PartFactory<Mixer>>& mixers();
 Registry<PartFactory<FeedForward>>& feed_forwards();
+Registry<PartFactory<Shift>>& shifts();
+Registry<PartFactory<TokenInput>>& token_inputs();
 Registry<ArrangementFactory>& arrangements();
 
 // Registers the library's own parts (idempotent; called before any model is built).

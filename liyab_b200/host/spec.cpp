@@ -24,6 +24,8 @@ const char* role_name(Role r) {
         case Role::Norm: return "norm";
         case Role::Mixer: return "mixer";
         case Role::FeedForward: return "feed_forward";
+        case Role::Shift: return "shift";
+        case Role::TokenInput: return "token_input";
     }
     return "?";
 }
@@ -32,7 +34,9 @@ Role role_from_name(const std::string& name) {
     if (name == "norm") return Role::Norm;
     if (name == "mixer") return Role::Mixer;
     if (name == "feed_forward") return Role::FeedForward;
-    throw invalid_model("unknown slot role '{}' (norm, mixer or feed_forward)", name);
+    if (name == "shift") return Role::Shift;
+    if (name == "token_input") return Role::TokenInput;
+    throw invalid_model("unknown slot role '{}' (norm, mixer, feed_forward, shift or token_input)", name);
 }
 
 const SlotSpec* LayerSpec::find(const std::string& name) const {

@@ -33,7 +33,9 @@ struct PartSpec {
     static PartSpec from_json(const Json& j, const std::string& what);
 };
 
-enum class Role { Norm, Mixer, FeedForward };
+// Shift: a blend of the mixer's input with the row before it (state per request).  TokenInput: an addition to the
+// residual stream made from the step's token ids (a side table), after the block's other parts.
+enum class Role { Norm, Mixer, FeedForward, Shift, TokenInput };
 const char* role_name(Role r);
 Role role_from_name(const std::string& name);
 
