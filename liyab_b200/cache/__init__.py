@@ -25,6 +25,7 @@ class KvNeed:
     n_kv_head: int
     head_dim: int
     window: int = 0          # 0: every position is kept; w: the w latest positions
+    planes: int = 2          # rows per position and head: 2 (a key and a value) or 1 (one row that serves as both)
 
 
 @dataclass(frozen=True)
@@ -55,9 +56,9 @@ class CacheManager:
         if _borrowed is not None:
             self._h = _borrowed
         else:
-            needs = {"kv": {str(u): [n.n_kv_head, n.head_dim, n.window] for u, n in (kv_needs or {}).items()},
+            needs = {"kv": {str(u): [n.n_kv_head, n.head_dim, n.window, n.planes] for u, n in (kv_needs or {}).items()},
                      "state": {str(u): {"shape": list(n.shape), "dtype": n.dtype} for u, n in (state_needs or {}).items()},
-                     "pages_per_group": [[n.n_kv_head, n.head_dim, n.window, p] for n, p in (pages_per_group or {}).items()]}
+                     "pages_per_group": [[n.n_kv_head, n.head_dim, n.window, p, n.planes] for n, p in (pages_per_group or {}).items()]}
             h = C.c_void_p()
             _capi.check(self._lib.lb_cache_create(_capi.b(json.dumps(needs)), page_size, num_pages, max_requests, C.byref(h)))
             self._h = h

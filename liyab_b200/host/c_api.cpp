@@ -438,7 +438,7 @@ int32_t lb_cache_create(const char* needs_json, int32_t page_size, int32_t num_p
         if (const Json* k = j.find("kv"))
             for (const auto& m : k->members()) {
                 const auto v = m.second.int_list();
-                kv[std::stoi(m.first)] = KvNeed{static_cast<int>(v.at(0)), static_cast<int>(v.at(1)), static_cast<int>(v.at(2))};
+                kv[std::stoi(m.first)] = KvNeed{static_cast<int>(v.at(0)), static_cast<int>(v.at(1)), static_cast<int>(v.at(2)), v.size() > 3 ? static_cast<int>(v[3]) : 2};
             }
         if (const Json* s = j.find("state"))
             for (const auto& m : s->members()) {
@@ -450,7 +450,7 @@ int32_t lb_cache_create(const char* needs_json, int32_t page_size, int32_t num_p
         if (const Json* p = j.find("pages_per_group"))
             for (const auto& e : p->items()) {
                 const auto v = e.int_list();
-                per_group[KvNeed{static_cast<int>(v.at(0)), static_cast<int>(v.at(1)), static_cast<int>(v.at(2))}] = static_cast<int>(v.at(3));
+                per_group[KvNeed{static_cast<int>(v.at(0)), static_cast<int>(v.at(1)), static_cast<int>(v.at(2)), v.size() > 4 ? static_cast<int>(v[4]) : 2}] = static_cast<int>(v.at(3));
             }
         auto h = std::make_unique<lb_cache>();
         h->owned = std::make_unique<CacheManager>(kv, state, page_size, num_pages, max_requests, DType::F32, false, per_group);
@@ -469,7 +469,7 @@ int32_t lb_cache_describe(const lb_cache* c, char* buffer, size_t size, size_t* 
         Json groups = Json::array();
         for (const auto& g : c->cache->groups)
             groups.push(Json::object().set("units", Json::array_of(g.units)).set("n_kv_head", g.need.n_kv_head).set("head_dim", g.need.head_dim)
-                            .set("window", g.need.window).set("num_pages", g.pool.num_pages()).set("page_size", g.page_size));
+                            .set("window", g.need.window).set("planes", g.need.planes).set("num_pages", g.pool.num_pages()).set("page_size", g.page_size));
         Json unit_groups = Json::object();
         for (const auto& [u, g] : c->cache->group_of_unit) unit_groups.set(std::to_string(u), g);
         Json open = Json::object();

@@ -100,8 +100,9 @@ def token_side(x, tokens, W, layer, dim, eps):
     return x + rms(y, eps) * W[p + "norm"]
 
 
-def forward(config, weights, tokens, return_layers=False):
-    """Logits [n, vocab] of a whole sequence (and the residual stream after every layer)."""
+def forward(config, weights, tokens, return_layers=False, trace=None):
+    """Logits [n, vocab] of a whole sequence (and the residual stream after every layer).  `trace`, a list, receives
+    (name, rows) after every mechanism of every layer."""
     W = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
     tokens = np.asarray(tokens, dtype=np.int64)
     eps, groups = config["norm"]["eps"], config["norm"]["groups"]
@@ -111,18 +112,24 @@ def forward(config, weights, tokens, return_layers=False):
     for i, layer in enumerate(config["layers"]):
         assert layer["type"] == "latent_attention"
         m = layer["mixer"]
+        note = (lambda name, rows: trace.append((name, rows.copy()))) if trace is not None else (lambda name, rows: None)
         h = grouped_rms_norm(x, W[f"l{i}.norm1"], groups, eps)
+        note("norm", h)
         hm = token_shift(h, W[f"l{i}.shift"])
+        note("shift", hm)
         if m.get("kv_from") is None:
             kept[i] = latent_and_key(hm, W, f"l{i}.mix.", m, eps)
         c, kr = kept[i if m.get("kv_from") is None else m["kv_from"]]
         y = latent_attention(hm, W, f"l{i}.mix.", m, c, kr)
+        note("mixer", x + y)
         if layer.get("mlp") is not None:
             assert layer["mlp"]["kind"] == "dense"
             y = y + dense_ff(h, W, f"l{i}.mlp.")
+            note("feed_forward", x + y)
         x = x + y
         if config.get("token_side") is not None:
             x = token_side(x, tokens, W, i, config["token_side"]["dim"], eps)
+            note("token_input", x)
         after.append(x.copy())
     logits = grouped_rms_norm(x, W["final.norm"], groups, eps) @ W["embed"].T
     return (logits, np.stack(after)) if return_layers else logits
