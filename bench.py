@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--size small] [--layers L] [--dtype bfloat16]
     python bench.py --impl reference        # the reference's own tools on this machine's CPU, or why they cannot run
+    python bench.py --design puzutar [--size small]   # Puzutar at GPT-2's layer sizes beside GPT-2 itself (see puzutar_line)
 
 A step is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (12 layers, width 768, 12 heads) with random weights, a batch of
@@ -203,6 +204,88 @@ def size_block(tmp, size, dtype, steps, pk):
     return block, folder
 
 
+def puzutar_config(size, layers=0):
+    """Puzutar with the width, depth, head count, inner width and vocabulary of a GPT-2 size: heads of 48 unrotated and
+    16 rotated query values and 64 value values (GPT-2's head size), a latent of a third of the width rounded up to 128,
+    a window of 512, two norm groups, a side input of 64 values; of every four blocks the last two read the second's latent."""
+    g = SIZES[size]
+    L, W, H = layers or g["n_layer"], g["n_embd"], g["n_head"]
+    rank = max(128, (W // 3 + 127) // 128 * 128)
+    blocks = []
+    for i in range(L):
+        m = dict(heads=H, dim=48, rot_dim=16, vdim=64, kv_rank=rank, scale=0.125, mask=dict(size=512), rot=dict(base=1e6, dims=16))
+        if i % 4 >= 2:
+            m["kv_from"] = i - i % 4 + 1
+        blocks.append(dict(type="latent_attention", mixer=m, mlp=dict(kind="dense", ff=g["n_inner"])))
+    return dict(architecture="Puzutar", vocab=g["vocab_size"], width=W, norm=dict(eps=1e-5, groups=2), token_side=dict(dim=64),
+                max_positions=g["n_positions"], layers=blocks)
+
+
+def puzutar_bytes_and_flops(cfg, dtype_bytes):
+    W, V, side = cfg["width"], cfg["vocab"], cfg["token_side"]["dim"]
+    weights, per_pos_read, per_token, attn = V * W, 0, 0, []
+    for l in cfg["layers"]:
+        m, ff = l["mixer"], l["mlp"]["ff"]
+        H, dq, rank, rot = m["heads"], m["dim"] + m["rot_dim"], m["kv_rank"], m["rot_dim"]
+        mats = H * dq * W + (0 if "kv_from" in m else (rank + rot) * W) + H * m["dim"] * rank + H * m["vdim"] * rank + W * H * m["vdim"] + 2 * W * ff + 2 * side * W
+        weights += mats
+        per_token += mats
+        per_pos_read += rank + rot                   # every block reads its (own or borrowed) latent rows once per request and step
+        attn.append((H, rank, rot, m["mask"]["size"]))
+
+    def prefill_flops(seq_lens, rows):
+        total = 2 * sum(seq_lens) * per_token + 2 * rows * V * W
+        for H, rank, rot, w in attn:                 # scores over rank + rot values and sums over rank values, on the latent rows
+            total += sum(2 * H * (2 * rank + rot) * sum(min(i + 1, w) for i in range(s)) for s in seq_lens)
+        return total
+
+    return dtype_bytes * (weights + side * 0), dtype_bytes * per_pos_read, prefill_flops, [w for _, _, _, w in attn]
+
+
+def puzutar_line(args) -> int:
+    """--design puzutar: decode (batch 1 / 8 / 64, 512-token prompts) and prefill (2 x 1024 tokens) of Puzutar at the layer
+    sizes of GPT-2 `--size`, and the same four figures of GPT-2 at that size, device-timed by the library's own measurement."""
+    from liyab_b200.engine import Replayer
+    from liyab_b200.weights import write_random_model
+    pk = peaks()
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    cfg = puzutar_config(args.size, args.layers)
+    gpt = dict(SIZES[args.size], n_layer=args.layers or SIZES[args.size]["n_layer"])
+    steps = min(args.steps, 128)
+    out = {"design": "puzutar", "size": args.size, "dtype": args.dtype, "peaks": pk["source"],
+           "config": {k: cfg[k] for k in ("width", "vocab", "norm", "token_side")} | {"layers": len(cfg["layers"]), "mixer": cfg["layers"][0]["mixer"],
+                                                                                     "ff": cfg["layers"][0]["mlp"]["ff"]}}
+    with tempfile.TemporaryDirectory(prefix="liyab_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "puzutar"), cfg, seed=0, dtype=args.dtype)
+        rep = Replayer(folder, args.dtype, max_tokens=64 * 1024, max_requests=64, cuda_graphs=True, max_step_tokens=PREFILL_TOKENS)
+        weight_bytes, row_bytes, flops, windows = puzutar_bytes_and_flops(cfg, dtype_bytes)
+        block = {}
+        for b in (1, 8, 64):
+            r = rep.bench_decode(b, PROMPT_LEN, steps, 3, 0)
+            seen = sum(min(r["mean_context"], w) for w in windows) / len(windows)
+            step_bytes = weight_bytes + b * seen * row_bytes
+            achieved = step_bytes / (r["ms_per_step"] / 1e3) / 1e9
+            r.update(tok_s=b / (r["ms_per_step"] / 1e3), frac=achieved / pk["hbm_gbs"])
+            block[f"decode_b{b}"] = detail(r) | {"launches_per_step": r["kernel_launches"] // steps}
+        n_seq = PREFILL_TOKENS // 1024
+        r = rep.bench_prefill(n_seq, 1024, 5)
+        peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else FP32_TFLOPS_NOMINAL
+        block["prefill"] = {"value": round(PREFILL_TOKENS / (r["ms_per_step"] / 1e3), 1), "ms": round(r["ms_per_step"], 4),
+                            "frac": round(flops([1024] * n_seq, n_seq) / (r["ms_per_step"] / 1e3) / 1e12 / peak, 4), "launches": r["kernel_launches"]}
+        rep.close()
+        out["puzutar"] = block
+        out["gpt2"], _ = size_block(tmp, args.size, args.dtype, steps, pk) if not args.layers else ({}, None)
+        if args.layers:
+            gfolder = write_random_model(os.path.join(tmp, "gpt2"), gpt, seed=0, dtype=args.dtype)
+            grep_ = Replayer(gfolder, args.dtype, max_tokens=64 * 1024, max_requests=64, cuda_graphs=True, max_step_tokens=PREFILL_TOKENS)
+            gb = {f"decode_b{b}": detail(decode_point(grep_, gpt, dtype_bytes, b, steps, 3, pk)) for b in (1, 8, 64)}
+            gb["prefill"] = prefill_point(grep_, gpt, dtype_bytes, pk, args.dtype)
+            grep_.close()
+            out["gpt2"] = gb
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(args) -> int:
     from baseline.reference_arm import run
     return run(args)
@@ -220,9 +303,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="the headline figure only")
     ap.add_argument("--no-extra", action="store_true", help="skip the 32-bit engine, the other sizes and the mixed workload")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar"],
+                    help="puzutar: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design == "puzutar":
+        return puzutar_line(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (run with --gpus 1)")
         return 2

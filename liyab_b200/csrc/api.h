@@ -185,8 +185,8 @@ int lb_token_side(int dtype, float* x, int64_t ldx, const int32_t* tokens, const
 int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
                     const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps, void* stream);
 /* Queries [T, H * (dim + rot)], head by head [dim | rot]: the rot part, rotated as above, goes to columns
- * h * (rank + rot) + rank .. of the wide queries (float). */
-int lb_rope_heads(int q_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, float* wide, int64_t ldw,
+ * h * (rank + rot) + rank .. of the wide queries (built: float queries to float or bfloat16 wide queries). */
+int lb_rope_heads(int q_dtype, int wide_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, void* wide, int64_t ldw,
                   int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, void* stream);
 /* C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n], n < N, k < K, for every head h;
  * 32-bit FMA whatever the element types (built: f32 f32 f32; bf16 bf16 f32; f32 bf16 bf16; f32 bf16 f32). */
@@ -197,6 +197,15 @@ int lb_head_matmul(int a_dtype, int b_dtype, int c_dtype, const void* A, int64_t
 int lb_latent_attention(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
                         const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
                         int n_head, int rank, int rot, int page_size, float scale, int window, void* stream);
+/* The same attention on the tensor cores for bfloat16 wide queries and cache rows (lb_latent_attention_mma_supports: rank one of
+ * 32, 64, 96, 128, 192, 256, 384, 512; rot a multiple of 16).  Request i brings rows q_start[i] .. q_start[i + 1] - 1, the first at
+ * position n_past[i]; max_q_len is the longest such run.  n_splits > 1 cuts every request's keys over that many blocks; it needs
+ * part_o (n_splits * n_tokens * n_head * rank floats) and part_ml (n_splits * n_tokens * n_head * 2 floats), merged by a second launch. */
+int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size);
+int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                            const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
+                            int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
+                            int n_splits, void* stream);
 
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw

@@ -53,9 +53,9 @@ __global__ void latent_store_kernel(const float* __restrict__ d, int64_t ldd, co
 }
 
 // q: [T, H * (dim + rot)], head by head [dim | rot]; wide: [T, H * (rank + rot)] float, head by head [rank | rot].
-template <typename T>
+template <typename T, typename TW>
 __global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const float* __restrict__ freq, const int32_t* __restrict__ positions,
-                                  float* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims, int rank) {
+                                  TW* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims, int rank) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int t = blockIdx.x, p = positions[t], half = rot_dims / 2;
@@ -63,14 +63,14 @@ __global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const fl
     for (int idx = threadIdx.x; idx < n_head * per_head; idx += blockDim.x) {
         const int h = idx / per_head, i = idx - h * per_head;
         const T* in = q + (size_t)t * ldq + (size_t)h * (dim + rot) + dim;
-        float* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot) + rank;
+        TW* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot) + rank;
         if (i < half) {
             float u, v;
             rotate_pair(lb_to_float(in[i]), lb_to_float(in[half + i]), p, freq[i], &u, &v);
-            out[i] = u;
-            out[half + i] = v;
+            out[i] = lb_from_float<TW>(u);
+            out[half + i] = lb_from_float<TW>(v);
         } else {
-            out[rot_dims + i - half] = lb_to_float(in[rot_dims + i - half]);
+            out[rot_dims + i - half] = lb_from_float<TW>(lb_to_float(in[rot_dims + i - half]));
         }
     }
 }
@@ -262,19 +262,19 @@ extern "C" int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, con
     return LB_OK;
 }
 
-extern "C" int lb_rope_heads(int q_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, float* wide, int64_t ldw,
+extern "C" int lb_rope_heads(int q_dtype, int wide_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, void* wide, int64_t ldw,
                              int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, void* stream) {
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && dim >= 0 && rot >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rank > 0,
                  "rotation of queries: bad sizes heads=%d dim=%d rot=%d rotated=%d", n_head, dim, rot, rot_dims);
     if (n_tokens == 0 || rot == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
-    if (q_dtype == LB_F32)
-        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions, wide, ldw,
-                                           n_head, dim, rot, rot_dims, rank));
-    else if (q_dtype == LB_BF16)
-        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, (const __nv_bfloat16*)q, ldq, freq,
-                                           positions, wide, ldw, n_head, dim, rot, rot_dims, rank));
-    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "rotation of queries: unknown dtype %d", q_dtype);
+    if (q_dtype == LB_F32 && wide_dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float, float>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions,
+                                           (float*)wide, ldw, n_head, dim, rot, rot_dims, rank));
+    else if (q_dtype == LB_F32 && wide_dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float, __nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions,
+                                           (__nv_bfloat16*)wide, ldw, n_head, dim, rot, rot_dims, rank));
+    else return lb_fail(LB_ERR_UNSUPPORTED, "rotation of queries: element types %d -> %d are not built", q_dtype, wide_dtype);
     return LB_OK;
 }
 

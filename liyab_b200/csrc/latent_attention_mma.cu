@@ -1,0 +1,327 @@
+// Attention over latent cache rows on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit accumulation).
+//
+// The same computation as lb_latent_attention (latent_attention.cu): wide queries [T, H, rank + rot] against cache
+// rows [rank | rot], softmax in 32-bit, the weighted sum of the rows' first `rank` values out.  All heads share the
+// rows, so a block takes M = 16 * MT query rows that are (token, head) pairs of one request, HB heads of TOK = M / HB
+// consecutive tokens, and walks the visible keys in tiles of 32:
+//   scores   warp w makes the 8 keys 8w .. 8w + 7 of the tile for all M rows, k over rank + rot;
+//   softmax  row maxima and sums meet in shared memory; the weights go there too, as bfloat16;
+//   sums     warp w owns a quarter of the rank values of all M rows and adds weights x rows to them.
+// Key tiles arrive by cp.async, one tile ahead.  A request's keys may be split over several blocks (decode steps of
+// few requests); the parts are merged by a second kernel.  Shapes: rank a multiple of 32 from a built list, rot a
+// multiple of 16; anything else stays with the 32-bit kernel.
+#include "api.h"
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int kKeys = 32;
+constexpr int kPStride = kKeys + 8;          // weights' row stride in shared memory (elements): 80 bytes, conflict-free for ldmatrix
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// MT: 16-row tiles of a block; RT: 8-column tiles of the rank values per warp (rank = 32 * RT).
+template <int MT, int RT>
+__global__ void __launch_bounds__(128)
+latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
+                            const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride,
+                            float* __restrict__ out, int64_t ldo, float* __restrict__ part_o, float* __restrict__ part_ml, int n_tokens,
+                            int n_head, int rot, int page_size, float scale_log2, int window, int hb_log2, int n_splits) {
+    constexpr int M = 16 * MT, RANK = 32 * RT;
+    const int D = RANK + rot, DS = D + 8, chunks = D / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);               // [M][DS]
+    bf16* ks = qs + (size_t)M * DS;                              // [2][kKeys][DS]
+    bf16* ps = ks + (size_t)2 * kKeys * DS;                      // [M][kPStride]
+    float* red_max = reinterpret_cast<float*>(ps + (size_t)M * kPStride);   // [4][M]
+    float* red_sum = red_max + 4 * M;                            // [4][M]
+
+    const int HB = 1 << hb_log2, TOK = M >> hb_log2;
+    const int s = blockIdx.y, split = blockIdx.z % n_splits, hg = blockIdx.z / n_splits;
+    const int first = q_start[s] + blockIdx.x * TOK;
+    const int n_here = min(TOK, q_start[s + 1] - first);
+    if (n_here <= 0) return;
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int p_first = n_past[s] + blockIdx.x * TOK, p_last = p_first + n_here - 1;
+    const int lo_min = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int32_t* table = block_table + (size_t)s * table_stride;
+
+    // The block's tiles of keys, and this split's share of them.
+    const int tile_lo = lo_min / kKeys, tile_hi = p_last / kKeys;
+    const int per = (tile_hi - tile_lo + n_splits) / n_splits;
+    const int my_lo = tile_lo + split * per, my_hi = min(tile_hi, my_lo + per - 1);
+
+    // Queries: row r is token first + (r >> hb_log2), head hg * HB + (r & (HB - 1)).
+    for (int r = warp; r < M; r += 4) {
+        const int tok = r >> hb_log2, head = hg * HB + (r & (HB - 1));
+        const bool valid = tok < n_here && head < n_head;
+        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
+        }
+    }
+    auto load_tile = [&](int tile, int buf) {
+        bf16* dst0 = ks + (size_t)buf * kKeys * DS;
+        for (int key = warp; key < kKeys; key += 4) {
+            const int j = tile * kKeys + key;
+            bf16* dst = dst0 + (size_t)key * DS;
+            if (j >= lo_min && j <= p_last) {
+                const bf16* src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D;
+                for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 8, src + c * 8);
+            } else {
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float o[MT][RT][4];
+    float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        m_run[mt][0] = m_run[mt][1] = -CUDART_INF_F;
+        l_run[mt][0] = l_run[mt][1] = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < RT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.0f;
+    }
+
+    if (my_lo <= my_hi) load_tile(my_lo, 0);
+    for (int tile = my_lo; tile <= my_hi; ++tile) {
+        const int buf = (tile - my_lo) & 1;
+        cp_async_wait_all();
+        __syncthreads();                                        // the tile (and, first time, the queries) is there; the step before is over
+        if (tile < my_hi) load_tile(tile + 1, buf ^ 1);
+        const bf16* kt = ks + (size_t)buf * kKeys * DS;
+
+        // ---- scores of keys 8w .. 8w + 7 for all rows
+        float sc[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[mt][i] = 0.0f;
+        for (int kk = 0; kk < D; kk += 16) {
+            uint32_t b[2];
+            ldmatrix_x2(b, kt + (size_t)(8 * warp + (lane & 7)) * DS + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4(a, qs + (size_t)(mt * 16 + (lane & 15)) * DS + kk + (lane >> 4) * 8);
+                mma_bf16(sc[mt], a, b);
+            }
+        }
+        // ---- mask, row maxima over the warp's keys
+        const int j0 = tile * kKeys + 8 * warp + 2 * t4;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = mt * 16 + g + 8 * half, tok = row >> hb_log2;
+                const int p_row = p_first + tok, lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
+                float mx = -CUDART_INF_F;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = j0 + e;
+                    const bool seen = tok < n_here && j >= lo_row && j <= p_row;
+                    const float v = seen ? sc[mt][2 * half + e] * scale_log2 : -CUDART_INF_F;
+                    sc[mt][2 * half + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                if (t4 == 0) red_max[warp * M + row] = mx;
+            }
+        __syncthreads();
+        // ---- weights (to shared memory as bfloat16), row sums, rescaling of what has been summed so far
+        float corr[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = mt * 16 + g + 8 * half;
+                const float m_tile = fmaxf(fmaxf(red_max[row], red_max[M + row]), fmaxf(red_max[2 * M + row], red_max[3 * M + row]));
+                const float m_new = fmaxf(m_run[mt][half], m_tile);
+                const bool none = m_new == -CUDART_INF_F;                   // nothing seen yet in this row
+                corr[mt][half] = none ? 1.0f : exp2f(m_run[mt][half] - m_new);
+                const float p0 = none ? 0.0f : exp2f(sc[mt][2 * half] - m_new), p1 = none ? 0.0f : exp2f(sc[mt][2 * half + 1] - m_new);
+                *reinterpret_cast<__nv_bfloat162*>(ps + (size_t)row * kPStride + 8 * warp + 2 * t4) = __floats2bfloat162_rn(p0, p1);
+                float sum = p0 + p1;
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (t4 == 0) red_sum[warp * M + row] = sum;
+                m_run[mt][half] = m_new;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = mt * 16 + g + 8 * half;
+                l_run[mt][half] = l_run[mt][half] * corr[mt][half] + ((red_sum[row] + red_sum[M + row]) + (red_sum[2 * M + row] + red_sum[3 * M + row]));
+            }
+#pragma unroll
+            for (int nt = 0; nt < RT; ++nt) {
+                o[mt][nt][0] *= corr[mt][0];
+                o[mt][nt][1] *= corr[mt][0];
+                o[mt][nt][2] *= corr[mt][1];
+                o[mt][nt][3] *= corr[mt][1];
+            }
+        }
+        // ---- weights x rows, this warp's quarter of the rank values
+#pragma unroll
+        for (int k2 = 0; k2 < kKeys; k2 += 16) {
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a[mt], ps + (size_t)(mt * 16 + (lane & 15)) * kPStride + k2 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nt = 0; nt < RT; ++nt) {
+                uint32_t b[2];
+                ldmatrix_x2_trans(b, kt + (size_t)(k2 + (lane & 15)) * DS + (warp * RT + nt) * 8);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) mma_bf16(o[mt][nt], a[mt], b);
+            }
+        }
+    }
+
+    // ---- out: normalised, or (keys split over blocks) the part with its maximum and sum
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = mt * 16 + g + 8 * half, tok = row >> hb_log2, head = hg * HB + (row & (HB - 1));
+            if (tok >= n_here || head >= n_head) continue;
+            const int t = first + tok;
+            if (n_splits == 1) {
+                const float inv = 1.0f / l_run[mt][half];
+                float* dst = out + (size_t)t * ldo + (size_t)head * RANK + warp * RT * 8 + 2 * t4;
+#pragma unroll
+                for (int nt = 0; nt < RT; ++nt)
+                    *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[mt][nt][2 * half] * inv, o[mt][nt][2 * half + 1] * inv);
+            } else {
+                const size_t at = ((size_t)split * n_tokens + t) * n_head + head;
+                float* dst = part_o + at * RANK + warp * RT * 8 + 2 * t4;
+#pragma unroll
+                for (int nt = 0; nt < RT; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[mt][nt][2 * half], o[mt][nt][2 * half + 1]);
+                if (warp == 0 && t4 == 0) {
+                    part_ml[at * 2] = m_run[mt][half];
+                    part_ml[at * 2 + 1] = l_run[mt][half];
+                }
+            }
+        }
+}
+
+// out[t, h, :] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the parts, in their order.
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out, int64_t ldo,
+                                    int n_tokens, int n_head, int rank, int n_splits) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, h = blockIdx.y;
+    float m = -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(((size_t)s * n_tokens + t) * n_head + h) * 2]);
+    float l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const size_t at = ((size_t)s * n_tokens + t) * n_head + h;
+        const float ms = part_ml[at * 2];
+        if (ms != -CUDART_INF_F) l += exp2f(ms - m) * part_ml[at * 2 + 1];
+    }
+    const float inv = 1.0f / l;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const size_t at = ((size_t)s * n_tokens + t) * n_head + h;
+            const float ms = part_ml[at * 2];
+            if (ms != -CUDART_INF_F) acc = fmaf(exp2f(ms - m), part_o[at * rank + d], acc);
+        }
+        out[(size_t)t * ldo + (size_t)h * rank + d] = acc * inv;
+    }
+}
+
+size_t mma_smem_bytes(int m, int rank, int rot) {
+    const int DS = rank + rot + 8;
+    return ((size_t)m * DS + (size_t)2 * kKeys * DS + (size_t)m * kPStride) * sizeof(bf16) + (size_t)8 * m * sizeof(float);
+}
+
+template <int MT, int RT>
+int launch_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
+               int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, int n_head, int rot,
+               int page_size, float scale, int window, int n_splits, cudaStream_t s) {
+    constexpr int M = 16 * MT;
+    int hb_log2 = 0;
+    while ((1 << hb_log2) < n_head && (1 << hb_log2) < M) ++hb_log2;
+    const int HB = 1 << hb_log2, TOK = M / HB;
+    const size_t smem = mma_smem_bytes(M, 32 * RT, rot);
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<MT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, ((n_head + HB - 1) / HB) * n_splits);
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_mma_kernel<MT, RT>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start,
+                                       n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_head, rot, page_size,
+                                       scale * 1.4426950408889634f, window, hb_log2, n_splits));
+    if (n_splits > 1)
+        LB_CHECK_CUDA(lb_launch_overlapped(latent_merge_kernel, dim3(n_tokens, n_head), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml, out, ldo,
+                                           n_tokens, n_head, 32 * RT, n_splits));
+    return LB_OK;
+}
+
+bool built_rank(int rank) {
+    for (const int r : {32, 64, 96, 128, 192, 256, 384, 512})
+        if (r == rank) return true;
+    return false;
+}
+
+}  // namespace
+
+extern "C" int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size) {
+    return n_head > 0 && built_rank(rank) && rot >= 0 && rot % 16 == 0 && page_size > 0 && mma_smem_bytes(32, rank, rot) <= 200 * 1024 ? 1 : 0;
+}
+
+extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                       const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
+                                       int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
+                                       int n_splits, void* stream) {
+    if (!lb_latent_attention_mma_supports(n_head, rank, rot, page_size))
+        return lb_fail(LB_ERR_UNSUPPORTED, "latent attention on tensor cores: rank %d, rot %d are not built", rank, rot);
+    LB_CHECK_ARG(n_tokens >= 0 && n_seq >= 0 && max_q_len >= 0 && n_splits >= 1 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+                 "latent attention: bad sizes tokens=%d requests=%d splits=%d", n_tokens, n_seq, n_splits);
+    if (n_tokens == 0 || n_seq == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    // Two 16-row tiles a block where a request brings several tokens and the sums still fit the registers; one otherwise.
+    const bool two = max_q_len > 1 && rank <= 256;
+#define LB_MMA(MT, RT) return launch_mma<MT, RT>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_seq, \
+                                                 max_q_len, n_head, rot, page_size, scale, window, n_splits, s)
+#define LB_MMA_RANK(RT)            \
+    if (rank == 32 * RT) {         \
+        if (two) LB_MMA(2, RT);    \
+        LB_MMA(1, RT);             \
+    }
+    LB_MMA_RANK(1) LB_MMA_RANK(2) LB_MMA_RANK(3) LB_MMA_RANK(4) LB_MMA_RANK(6) LB_MMA_RANK(8)
+    if (rank == 384) LB_MMA(1, 12);
+    if (rank == 512) LB_MMA(1, 16);
+#undef LB_MMA_RANK
+#undef LB_MMA
+    return lb_fail(LB_ERR_UNSUPPORTED, "latent attention on tensor cores: rank %d is not built", rank);
+}

@@ -313,16 +313,33 @@ void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float*
 }
 
 void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t* positions, const Rows& wide, int n_tokens, const LatentShape& a) {
-    if (wide.dtype != DType::F32 || wide.cols != static_cast<int64_t>(a.n_head) * (a.rank + a.rot) || q.cols != static_cast<int64_t>(a.n_head) * (a.dim + a.rot))
+    if (wide.cols != static_cast<int64_t>(a.n_head) * (a.rank + a.rot) || q.cols != static_cast<int64_t>(a.n_head) * (a.dim + a.rot))
         throw invalid_argument("rotation of queries: buffers do not fit");
-    check(lb_rope_heads(code(q.dtype, "q"), q.data, q.stride, freq, positions, wide.f32(), wide.stride, n_tokens, a.n_head, a.dim, a.rot, a.rot_dims,
-                        a.rank, s), "rope_heads");
+    check(lb_rope_heads(code(q.dtype, "q"), code(wide.dtype, "wide"), q.data, q.stride, freq, positions, wide.data, wide.stride, n_tokens, a.n_head, a.dim,
+                        a.rot, a.rot_dims, a.rank, s), "rope_heads");
 }
 
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
                  int64_t c_head, int m, int n, int k, int n_head) {
     check(lb_head_matmul(code(a.dtype, "a"), code(b.dtype, "b"), code(c.dtype, "c"), a.data, a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride,
                          c_head, m, n, k, n_head, s), "head_matmul");
+}
+
+bool latent_mma_supports(const LatentShape& a) { return lb_latent_attention_mma_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }
+
+int latent_splits(int n_seq, int n_head, int span) {
+    // Enough blocks for two waves of the GPU, but no part shorter than two tiles of 32 keys.
+    const int blocks = std::max(1, n_seq * ((n_head + 15) / 16)), tiles = span / 32 + 1;
+    return std::max(1, std::min({16, tiles / 2, (296 + blocks - 1) / blocks}));
+}
+
+void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
+                          int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
+                          int n_splits) {
+    if (wide.dtype != DType::BF16 || out.dtype != DType::F32) throw invalid_argument("latent attention on tensor cores: bfloat16 wide queries, float32 attended latents");
+    check(lb_latent_attention_mma(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.f32(), out.stride, part_o, part_ml, n_tokens,
+                                  n_seq, max_q_len, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, n_splits, s), "latent_attention_mma");
+    if (n_splits > 1) launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,

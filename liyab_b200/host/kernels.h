@@ -131,6 +131,13 @@ void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t*
 // C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n].
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
                  int64_t c_head, int m, int n, int k, int n_head);
+// The tensor-core kernel (bfloat16 wide queries and cache): whether it takes the shape, into how many parts a decode step's keys are cut
+// (a function of the step's shape and the longest span a query can see, so a recorded step and an eager one cut alike), and the launch.
+bool latent_mma_supports(const LatentShape& a);
+int latent_splits(int n_seq, int n_head, int span);
+void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
+                          int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
+                          int n_splits);
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
                       const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a);
 

@@ -134,7 +134,9 @@ public:
         proj.forward(ctx, h, qd, T);
         if (own_latent) kernels::latent_store(s, qd.columns(q_cols, D), latent_gain, freq, ctx.positions, view->slot_mapping, cache, dt, T, shape, eps);
         const Rows q = qd.columns(0, q_cols);
-        const Rows wide = ws.get("latent.wide", T, static_cast<int64_t>(a.n_head) * D, DType::F32);
+        // bfloat16 and a shape the tensor-core kernel takes: wide queries in bfloat16 for it; else 32-bit throughout.
+        const bool tensor = dt == DType::BF16 && kernels::latent_mma_supports(shape);
+        const Rows wide = ws.get(tensor ? "latent.wide16" : "latent.wide", T, static_cast<int64_t>(a.n_head) * D, tensor ? DType::BF16 : DType::F32);
         kernels::rope_heads(s, q, freq, ctx.positions, wide, T, shape);
         if (a.dim > 0)
             kernels::head_matmul(s, q, a.dim + a.rot, uk, static_cast<int64_t>(a.dim) * a.rank, a.rank, 1, wide, D, T, a.rank, a.dim, a.n_head);
@@ -142,7 +144,20 @@ public:
             LIYAB_CUDA(cudaMemset2DAsync(wide.data, static_cast<size_t>(wide.stride) * 4, 0, static_cast<size_t>(wide.cols) * 4, static_cast<size_t>(T), s));
         ctx.tap("latent.wide", wide);
         const Rows attended = ws.get("latent.attended", T, static_cast<int64_t>(a.n_head) * a.rank, DType::F32);
-        kernels::latent_attention(s, dt, wide, cache, ctx.tok_seq, ctx.positions, view->block_table, view->table_width, attended, T, shape);
+        if (tensor) {
+            // A decode step's keys are cut over several blocks so that a few requests still fill the GPU.
+            const int span = a.window > 0 ? std::min(a.window, ctx.max_positions) : ctx.max_positions;
+            const int splits = ctx.decode_only ? kernels::latent_splits(ctx.n_seq, a.n_head, span) : 1;
+            float *part_o = nullptr, *part_ml = nullptr;
+            if (splits > 1) {
+                part_o = static_cast<float*>(ws.flat("latent.part", static_cast<int64_t>(splits) * T * a.n_head * a.rank, DType::F32));
+                part_ml = static_cast<float*>(ws.flat("latent.part_ml", static_cast<int64_t>(splits) * T * a.n_head * 2, DType::F32));
+            }
+            kernels::latent_attention_mma(s, wide, cache, ctx.q_start, ctx.n_past, view->block_table, view->table_width, attended, part_o, part_ml, T,
+                                          ctx.n_seq, ctx.max_q_len, shape, splits);
+        } else {
+            kernels::latent_attention(s, dt, wide, cache, ctx.tok_seq, ctx.positions, view->block_table, view->table_width, attended, T, shape);
+        }
         const Rows values = ws.get("latent.values", T, static_cast<int64_t>(a.n_head) * a.vdim, dt);
         kernels::head_matmul(s, attended, a.rank, uv, static_cast<int64_t>(a.vdim) * a.rank, 1, a.rank, values, a.vdim, T, a.vdim, a.rank, a.n_head);
         ctx.tap("attention", values);

@@ -351,8 +351,10 @@ void write_random_model(const std::string& model_dir, const ArchitectureConfig& 
     }
     struct Item { std::string name; std::vector<int64_t> shape; double mean, std; std::vector<uint8_t> bytes; };
     std::vector<Item> items;
+    std::set<std::string> written;          // a file tensor may feed several parameters (slices of one table)
     for (const auto& [dest, spec] : config.checkpoint_map())
-        for (const auto& src : spec.sources) items.push_back({src.name, src.shape, spec.init_mean, spec.init_std, {}});
+        for (const auto& src : spec.sources)
+            if (written.insert(src.name).second) items.push_back({src.name, src.shape, spec.init_mean, spec.init_std, {}});
     const size_t es = dtype_size(store);
     // Large tensors are cut into pieces so that every core has work.
     struct Piece { size_t item; int64_t first, count; };

@@ -2,7 +2,7 @@
 
 P differs from layer to layer in every size the design has (heads, head sizes, latent size, window, rotated
 share, feed-forward or none) and has two blocks that read another block's latent rows with windows of their own.
-Q has one norm group, no side input, no window, a head count that no kernel tile divides and a latent wider than
+T has the sizes that the tensor-core attention kernel takes.  Q has one norm group, no side input, no window, a head count that no kernel tile divides and a latent wider than
 128.  R keeps three sizes equal to one (a head count, a head size, the side input's width), norm groups of four
 values, and two blocks on one latent whose windows end one before and on a page border.
 """
@@ -44,7 +44,15 @@ CONFIG_R = dict(architecture="Puzutar", vocab=64, width=48, norm=dict(eps=1e-5, 
     layer(mixer(4, 12, 4, 12, 8, 31, scale=0.7), 48),
     layer(mixer(4, 12, 4, 12, 8, 32, scale=0.7, kv_from=1), 48),
 ])
-CONFIGS = {"P": (CONFIG_P, 11), "Q": (CONFIG_Q, 12), "R": (CONFIG_R, 13)}
+# Shapes that the bfloat16 engine's tensor-core attention takes (latents of 32, 64 and 96 values, rotated parts of 16 and 32): fewer
+# heads than a row tile, more than one (two head groups), a reader with a window of its own, and one block without a window.
+CONFIG_T = dict(architecture="Puzutar", vocab=200, width=128, norm=dict(eps=1e-5, groups=4), token_side=dict(dim=16), layers=[
+    layer(mixer(12, 16, 16, 16, 64, 40), 256),
+    layer(mixer(3, 8, 16, 24, 64, 70, kv_from=0), 128),
+    layer(mixer(20, 8, 32, 8, 96, 0, base=1e5), 128),
+    layer(mixer(2, 32, 16, 32, 32, 33), 0),
+])
+CONFIGS = {"P": (CONFIG_P, 11), "Q": (CONFIG_Q, 12), "R": (CONFIG_R, 13), "T": (CONFIG_T, 14)}
 
 
 def to_bf16_values(a):

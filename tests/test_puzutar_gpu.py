@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # float32: largest |engine - plain| on a logit as a fraction of the largest |logit| of the sequence.
 REL_TOL = {"float32": 3e-5}
-LENGTHS = {"P": [150, 70, 33, 21, 7, 2, 1, 45], "Q": [130, 41, 64, 3, 1, 17], "R": [100, 33, 32, 31, 2, 65]}
+LENGTHS = {"P": [150, 70, 33, 21, 7, 2, 1, 45], "Q": [130, 41, 64, 3, 1, 17], "R": [100, 33, 32, 31, 2, 65], "T": [140, 72, 31, 1, 2, 97, 40]}
 
 
 def tokens_of(name, i, n):
@@ -68,7 +68,7 @@ def check(got, want, dtype):
     return {"mean": float(errs.mean()), "worst": float(errs.max())}
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_every_mechanism_by_itself(name, models):
     """The parts' outputs, layer by layer, against the plain functions in float32: norm in groups, token shift, the
     mixer, the feed-forward, the side input.  A whole prompt, then the same prompt cut in two (state and cache)."""
@@ -101,7 +101,7 @@ def test_every_mechanism_by_itself(name, models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_every_cutting_matches_plain(name, dtype, models, oracle):
     path, config, _ = models[name]
     reqs = request_set(name)
