@@ -174,9 +174,15 @@ int lb_rms_shift(int dtype, const float* x, int64_t ldx, const float* weight, co
 /* In place: z > 0 -> a z^2 + z/2, else b (exp(z) - 1 - z) + z/2, a = softplus(pq[0]), b = 1/2 + softplus(pq[1]). */
 int lb_xielu(int dtype, void* z, int64_t ldz, int n_rows, int cols, const float* pq, void* stream);
 /* x[t,:] += rms(y) * weight with y = proj . (gelu_tanh(gate . x[t,:]) * table[tokens[t],:]); gate [dim, width], proj
- * [width, dim] and table [vocab, dim] are `dtype`, x and weight float; rms divides by sqrt(mean(y^2) + eps). */
+ * [width, dim] and table [vocab, dim] are `dtype`, x and weight float; rms divides by sqrt(mean(y^2) + eps).  g: scratch of
+ * n_tokens * dim floats (two launches: the gate spread over the GPU, then a block per token). */
 int lb_token_side(int dtype, float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* gate, const void* proj,
-                  const float* weight, int n_tokens, int width, int dim, float eps, void* stream);
+                  const float* weight, float* g, int n_tokens, int width, int dim, float eps, void* stream);
+/* The pieces of the same for many tokens, around two library products (x16 . gate^T and g16 . proj^T):
+ * y[r, :] = bfloat16(x[r, :]);  g16[t, :] = bfloat16(gelu_tanh(pre[t, :]) * table[tokens[t], :]);  x[t, :] += rms(y[t, :]) * weight. */
+int lb_rows_to_bf16(const float* x, int64_t ldx, void* y, int64_t ldy, int n_rows, int cols, void* stream);
+int lb_side_gate_finish(const float* pre, int64_t ldp, const int32_t* tokens, const void* table, void* g16, int64_t ldg, int n_tokens, int dim, void* stream);
+int lb_rms_add(float* x, int64_t ldx, const float* y, int64_t ldy, const float* weight, int n_rows, int width, float eps, void* stream);
 
 /* Attention over a cache of latent rows [c (rank) | r (rot)], one row per position: pages [page][slot][rank + rot].
  * lb_latent_store: row t of d (float, [rank | rot]) -> c = d[:rank] / sqrt(mean^2 + eps) * gain; r = the last rot values
@@ -197,15 +203,31 @@ int lb_head_matmul(int a_dtype, int b_dtype, int c_dtype, const void* A, int64_t
 int lb_latent_attention(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
                         const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
                         int n_head, int rank, int rot, int page_size, float scale, int window, void* stream);
+/* Steps of few tokens, bfloat16 weights, cache and wide queries: lb_rope_heads, the keys' product per head (uk: [n_head * dim, rank]) and,
+ * with cache given, lb_latent_store in one launch; qd rows are [queries | latent row] floats (the latent row only with cache). */
+int lb_latent_few_supports(int dim, int rot, int rank, int vdim, int n_splits);
+int lb_latent_prepare(const float* qd, int64_t ldq, const void* uk, const float* gain, const float* freq, const int32_t* positions,
+                      const int32_t* slot_mapping, void* cache, void* wide, int64_t ldw, int n_tokens, int n_head, int dim, int rot, int rot_dims,
+                      int rank, float eps, void* stream);
+/* The merge of a split attention's parts (n_splits > 1; else `attended` is read) and the values' product per head (uv: [n_head * vdim, rank])
+ * in one launch; values bfloat16. */
+int lb_latent_finish(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values, int64_t ldv,
+                     int n_tokens, int n_head, int rank, int vdim, int n_splits, void* stream);
+/* lb_head_matmul on the tensor cores: A float (rounded to bfloat16 on the way in), B and C bfloat16; lb_head_matmul_mma_supports says
+ * whether the strides fit its 16-byte pieces (one of b_k, b_n is 1). */
+int lb_head_matmul_mma_supports(int64_t lda, int64_t a_head, int64_t b_head, int64_t b_k, int64_t b_n, int64_t ldc, int64_t c_head, int N, int K);
+int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
+                       int64_t c_head, int M, int N, int K, int n_head, void* stream);
 /* The same attention on the tensor cores for bfloat16 wide queries and cache rows (lb_latent_attention_mma_supports: rank one of
  * 32, 64, 96, 128, 192, 256, 384, 512; rot a multiple of 16).  Request i brings rows q_start[i] .. q_start[i + 1] - 1, the first at
  * position n_past[i]; max_q_len is the longest such run.  n_splits > 1 cuts every request's keys over that many blocks; it needs
- * part_o (n_splits * n_tokens * n_head * rank floats) and part_ml (n_splits * n_tokens * n_head * 2 floats), merged by a second launch. */
+ * part_o (n_splits * n_tokens * n_head * rank floats) and part_ml (n_splits * n_tokens * n_head * 2 floats), merged by a second launch
+ * (or, with merge_parts 0, left for lb_latent_finish; one part is always written to out as it is). */
 int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size);
 int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
                             const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
                             int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
-                            int n_splits, void* stream);
+                            int n_splits, int merge_parts, void* stream);
 
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw

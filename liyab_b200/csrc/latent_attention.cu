@@ -75,6 +75,133 @@ __global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const fl
     }
 }
 
+// Steps of few tokens (bfloat16): everything between the projection and the attention in one launch.  Block (t, h) widens head h's
+// query of token t: the rotated part as rope_heads_kernel does; the unrotated part through the keys' map uk_h [dim, rank], which
+// the block first brings into shared memory in 16-byte pieces (all requests in flight at once), then a thread per latent value.
+// Block (t, n_head), where the part has a latent of its own, stores the token's cache row as latent_store_kernel does.
+__global__ void __launch_bounds__(128)
+latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bfloat16* __restrict__ uk, const float* __restrict__ gain,
+                      const float* __restrict__ freq, const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
+                      __nv_bfloat16* __restrict__ cache, __nv_bfloat16* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims,
+                      int rank, float eps, int q_cols) {
+    extern __shared__ __align__(16) unsigned char prep_sm[];
+    __nv_bfloat16* map = reinterpret_cast<__nv_bfloat16*>(prep_sm);                     // [dim][rank]
+    float* qsm = reinterpret_cast<float*>(prep_sm + (((size_t)dim * rank * 2 + 15) & ~(size_t)15));     // the head's query [dim + rot]
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, h = blockIdx.y, half = rot_dims / 2;
+    if (h < n_head) {                          // the map does not depend on the kernel before: asked for ahead of the wait
+        const uint4* src = reinterpret_cast<const uint4*>(uk + (size_t)h * dim * rank);
+        uint4* dst = reinterpret_cast<uint4*>(map);
+        for (int i = threadIdx.x; i < dim * rank / 8; i += blockDim.x) dst[i] = src[i];
+    }
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int p = positions[t];
+    if (h == n_head) {
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const float* in = qd + (size_t)t * ldq + q_cols;
+        __nv_bfloat16* out = cache + (size_t)slot * (rank + rot);
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+        const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)rank + eps);
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = __float2bfloat16_rn(in[i] * inv * gain[i]);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float u, v;
+            rotate_pair(in[rank + i], in[rank + half + i], p, freq[i], &u, &v);
+            out[rank + i] = __float2bfloat16_rn(u);
+            out[rank + half + i] = __float2bfloat16_rn(v);
+        }
+        for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = __float2bfloat16_rn(in[rank + i]);
+        return;
+    }
+    const float* q = qd + (size_t)t * ldq + (size_t)h * (dim + rot);
+    for (int i = threadIdx.x; i < dim + rot; i += blockDim.x) qsm[i] = q[i];
+    __syncthreads();
+    __nv_bfloat16* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float u, v;
+        rotate_pair(qsm[dim + i], qsm[dim + half + i], p, freq[i], &u, &v);
+        out[rank + i] = __float2bfloat16_rn(u);
+        out[rank + half + i] = __float2bfloat16_rn(v);
+    }
+    for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = __float2bfloat16_rn(qsm[dim + i]);
+    for (int n = threadIdx.x; n < rank; n += blockDim.x) {
+        float acc = 0.0f;
+        for (int d = 0; d < dim; ++d) acc = fmaf(qsm[d], __bfloat162float(map[(size_t)d * rank + n]), acc);
+        out[n] = __float2bfloat16_rn(acc);
+    }
+}
+
+// Steps of few tokens (bfloat16): everything between the attention and the output projection in one launch.  Block (t, h) merges the
+// parts of a split attention (or takes the attended latent as it is), then maps it through the values' map uv_h [vdim, rank]: a warp
+// per value, lanes along the latent in 16-byte pieces, four values' pieces in flight.
+__global__ void __launch_bounds__(128)
+latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                     const __nv_bfloat16* __restrict__ uv, __nv_bfloat16* __restrict__ values, int64_t ldv, int n_tokens, int n_head, int rank, int vdim,
+                     int n_splits) {
+    extern __shared__ float osm[];             // the attended latent [rank], then the parts' factors [n_splits]
+    float* factor = osm + rank;
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (n_splits > 1) {
+        if (warp == 0) {                       // factor_s = 2^(m_s - m) / sum_s 2^(m_s - m) l_s, parts in their order
+            float ms = -CUDART_INF_F, ls = 0.0f;
+            if (lane < n_splits) {
+                const float2 ml = *reinterpret_cast<const float2*>(part_ml + (((size_t)lane * n_tokens + t) * n_head + h) * 2);
+                ms = ml.x;
+                ls = ml.y;
+            }
+            const float m = lb_warp_max(ms);
+            const float e = ms == -CUDART_INF_F ? 0.0f : exp2f(ms - m);
+            float l = 0.0f;
+            for (int s = 0; s < n_splits; ++s) l += __shfl_sync(0xffffffffu, e * ls, s);
+            if (lane < n_splits) factor[lane] = e / l;
+        }
+        __syncthreads();
+        for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+            float acc = 0.0f;
+#pragma unroll 4
+            for (int s = 0; s < n_splits; ++s) acc = fmaf(factor[s], part_o[(((size_t)s * n_tokens + t) * n_head + h) * rank + d], acc);
+            osm[d] = acc;
+        }
+    } else {
+        for (int d = threadIdx.x; d < rank; d += blockDim.x) osm[d] = attended[(size_t)t * lda + (size_t)h * rank + d];
+    }
+    __syncthreads();
+    const int pieces = rank / 8;
+    // A warp's values in batches of eight; a batch's first pieces are all asked for before any is used.
+    for (int v0 = warp; v0 < vdim; v0 += 32) {
+        uint4 ahead[8];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const int v = v0 + 4 * b;
+            ahead[b] = make_uint4(0u, 0u, 0u, 0u);
+            if (v < vdim && lane < pieces) ahead[b] = *reinterpret_cast<const uint4*>(uv + ((size_t)h * vdim + v) * rank + lane * 8);
+        }
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const int v = v0 + 4 * b;
+            if (v >= vdim) break;                                  // uniform across the warp
+            const __nv_bfloat16* row = uv + ((size_t)h * vdim + v) * rank;
+            float acc = 0.0f;
+            for (int c = lane; c < pieces; c += 32) {
+                const uint4 raw = c == lane ? ahead[b] : *reinterpret_cast<const uint4*>(row + c * 8);
+                const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __bfloat1622float2(w[k]);
+                    acc = fmaf(f.x, osm[c * 8 + 2 * k], acc);
+                    acc = fmaf(f.y, osm[c * 8 + 2 * k + 1], acc);
+                }
+            }
+            acc = lb_warp_sum(acc);
+            if (lane == 0) values[(size_t)t * ldv + (size_t)h * vdim + v] = __float2bfloat16_rn(acc);
+        }
+    }
+}
+
 // C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n] for n < N, k < K.
 // Tiles of 32 rows x 64 columns, K in chunks of 32 added in ascending order: a row's sums do not depend on the batch.
 template <typename TA, typename TB, typename TC>
@@ -259,6 +386,40 @@ extern "C" int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, con
         LB_CHECK_CUDA(lb_launch_overlapped(latent_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, d, ldd, gain, freq, positions,
                                            slot_mapping, (__nv_bfloat16*)cache, rank, rot, rot_dims, eps));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "latent store: unknown dtype %d", cache_dtype);
+    return LB_OK;
+}
+
+// Whether the two launches for steps of few tokens take the shape: the keys' map of a head fits a block's shared memory and both maps
+// split into 16-byte pieces; at most 32 parts.
+extern "C" int lb_latent_few_supports(int dim, int rot, int rank, int vdim, int n_splits) {
+    return dim > 0 && rank % 8 == 0 && ((size_t)dim * rank) % 8 == 0 && (size_t)dim * rank * 2 + (size_t)(dim + rot) * 4 + 16 <= 200 * 1024 && vdim > 0 &&
+                   n_splits >= 1 && n_splits <= 32 ? 1 : 0;
+}
+
+extern "C" int lb_latent_prepare(const float* qd, int64_t ldq, const void* uk, const float* gain, const float* freq, const int32_t* positions,
+                                 const int32_t* slot_mapping, void* cache, void* wide, int64_t ldw, int n_tokens, int n_head, int dim, int rot, int rot_dims,
+                                 int rank, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_head < 65535 && dim >= 0 && rot >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rank > 0,
+                 "latent queries: bad sizes heads=%d dim=%d rot=%d rotated=%d", n_head, dim, rot, rot_dims);
+    if (n_tokens == 0) return LB_OK;
+    if (!lb_latent_few_supports(dim, rot, rank, 8, 2)) return lb_fail(LB_ERR_UNSUPPORTED, "latent queries: the keys' map of %d x %d values does not fit a block", dim, rank);
+    const dim3 grid(n_tokens, n_head + (cache != nullptr ? 1 : 0));
+    const size_t smem = (((size_t)dim * rank * 2 + 15) & ~(size_t)15) + (size_t)(dim + rot) * sizeof(float);
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_prepare_kernel, grid, dim3(128), smem, static_cast<cudaStream_t>(stream), qd, ldq,
+                                       (const __nv_bfloat16*)uk, gain, freq, positions, slot_mapping, (__nv_bfloat16*)cache, (__nv_bfloat16*)wide, ldw, n_head, dim,
+                                       rot, rot_dims, rank, eps, n_head * (dim + rot)));
+    return LB_OK;
+}
+
+extern "C" int lb_latent_finish(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values, int64_t ldv,
+                                int n_tokens, int n_head, int rank, int vdim, int n_splits, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_head <= 65535 && rank > 0 && rank % 8 == 0 && vdim > 0 && n_splits >= 1 && n_splits <= 32,
+                 "latent values: bad sizes heads=%d rank=%d vdim=%d parts=%d", n_head, rank, vdim, n_splits);
+    if (n_tokens == 0) return LB_OK;
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_finish_kernel, dim3(n_tokens, n_head), dim3(128), (size_t)(rank + 32) * sizeof(float), static_cast<cudaStream_t>(stream),
+                                       attended, lda, part_o, part_ml, (const __nv_bfloat16*)uv, (__nv_bfloat16*)values, ldv, n_tokens, n_head, rank, vdim,
+                                       n_splits));
     return LB_OK;
 }
 

@@ -2,7 +2,7 @@
 //
 // The same computation as lb_latent_attention (latent_attention.cu): wide queries [T, H, rank + rot] against cache
 // rows [rank | rot], softmax in 32-bit, the weighted sum of the rows' first `rank` values out.  All heads share the
-// rows, so a block takes M = 16 * MT query rows that are (token, head) pairs of one request, HB heads of TOK = M / HB
+// rows, so a block takes M = 16 * MT query rows that are (token, head) pairs of one request, HB <= 16 heads of TOK = M / HB
 // consecutive tokens, and walks the visible keys in tiles of 32:
 //   scores   warp w makes the 8 keys 8w .. 8w + 7 of the tile for all M rows, k over rank + rot;
 //   softmax  row maxima and sums meet in shared memory; the weights go there too, as bfloat16;
@@ -24,6 +24,13 @@ constexpr int kPStride = kKeys + 8;          // weights' row stride in shared me
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 __device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
@@ -47,7 +54,7 @@ __global__ void __launch_bounds__(128)
 latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
                             const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride,
                             float* __restrict__ out, int64_t ldo, float* __restrict__ part_o, float* __restrict__ part_ml, int n_tokens,
-                            int n_head, int rot, int page_size, float scale_log2, int window, int hb_log2, int n_splits) {
+                            int n_head, int rot, int page_size, float scale_log2, int window, int HB, int n_splits) {
     constexpr int M = 16 * MT, RANK = 32 * RT;
     const int D = RANK + rot, DS = D + 8, chunks = D / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -57,7 +64,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
     float* red_max = reinterpret_cast<float*>(ps + (size_t)M * kPStride);   // [4][M]
     float* red_sum = red_max + 4 * M;                            // [4][M]
 
-    const int HB = 1 << hb_log2, TOK = M >> hb_log2;
+    const int TOK = M / HB;                                      // rows beyond TOK * HB stay empty
     const int s = blockIdx.y, split = blockIdx.z % n_splits, hg = blockIdx.z / n_splits;
     const int first = q_start[s] + blockIdx.x * TOK;
     const int n_here = min(TOK, q_start[s + 1] - first);
@@ -74,9 +81,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
     const int per = (tile_hi - tile_lo + n_splits) / n_splits;
     const int my_lo = tile_lo + split * per, my_hi = min(tile_hi, my_lo + per - 1);
 
-    // Queries: row r is token first + (r >> hb_log2), head hg * HB + (r & (HB - 1)).
+    // Queries: row r is token first + r / HB, head hg * HB + r % HB.
     for (int r = warp; r < M; r += 4) {
-        const int tok = r >> hb_log2, head = hg * HB + (r & (HB - 1));
+        const int tok = r / HB, head = hg * HB + r % HB;
         const bool valid = tok < n_here && head < n_head;
         const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
         for (int c = lane; c < chunks; c += 32) {
@@ -142,7 +149,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int row = mt * 16 + g + 8 * half, tok = row >> hb_log2;
+                const int row = mt * 16 + g + 8 * half, tok = row / HB;
                 const int p_row = p_first + tok, lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
                 float mx = -CUDART_INF_F;
 #pragma unroll
@@ -214,7 +221,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            const int row = mt * 16 + g + 8 * half, tok = row >> hb_log2, head = hg * HB + (row & (HB - 1));
+            const int row = mt * 16 + g + 8 * half, tok = row / HB, head = hg * HB + row % HB;
             if (tok >= n_here || head >= n_head) continue;
             const int t = first + tok;
             if (n_splits == 1) {
@@ -234,6 +241,178 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
                 }
             }
         }
+}
+
+// The same attention for steps with runs of tokens and latents of up to 256 values: a block takes 64 rows, every warp 16 of them with
+// all 32 keys of a tile and all rank values.  Maxima and sums stay inside the warp (four lanes share a row), the weights pass from the
+// score accumulators straight into the next product's operand registers, and the only block-wide meeting is the change of key tiles.
+// N8: 8-column tiles of the rank values (rank = 8 * N8, N8 even).
+template <int N8>
+__global__ void __launch_bounds__(128)
+latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
+                             const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
+                             int64_t ldo, int n_head, int rot, int page_size, float scale_log2, int window, int HB) {
+    constexpr int M = 64, RANK = 8 * N8;
+    const int D = RANK + rot, DS = D + 8, chunks = D / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);               // [M][DS]
+    bf16* ks = qs + (size_t)M * DS;                              // [2][kKeys][DS]
+    const int TOK = M / HB;                                      // rows beyond TOK * HB stay empty
+    const int s = blockIdx.y, hg = blockIdx.z;
+    const int first = q_start[s] + blockIdx.x * TOK;
+    const int n_here = min(TOK, q_start[s + 1] - first);
+    if (n_here <= 0) return;
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int p_first = n_past[s] + blockIdx.x * TOK, p_last = p_first + n_here - 1;
+    const int lo_min = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int32_t* table = block_table + (size_t)s * table_stride;
+    const int tile_lo = lo_min / kKeys, tile_hi = p_last / kKeys;
+
+    for (int r = warp; r < M; r += 4) {
+        const int tok = r / HB, head = hg * HB + r % HB;
+        const bool valid = tok < n_here && head < n_head;
+        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
+        }
+    }
+    auto load_tile = [&](int tile, int buf) {
+        bf16* dst0 = ks + (size_t)buf * kKeys * DS;
+        for (int key = warp; key < kKeys; key += 4) {
+            const int j = tile * kKeys + key;
+            bf16* dst = dst0 + (size_t)key * DS;
+            if (j >= lo_min && j <= p_last) {
+                const bf16* src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D;
+                for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 8, src + c * 8);
+            } else {
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // This thread's two rows (g and g + 8 of the warp's sixteen): their tokens' positions and first visible keys.
+    int p_row[2], lo_row[2];
+    bool live[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int tok = (warp * 16 + g + 8 * half) / HB;
+        live[half] = tok < n_here;
+        p_row[half] = p_first + tok;
+        lo_row[half] = window > 0 ? max(0, p_row[half] - window + 1) : 0;
+    }
+    float o[N8][4];
+#pragma unroll
+    for (int nt = 0; nt < N8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nt][i] = 0.0f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.0f, 0.0f};
+
+    load_tile(tile_lo, 0);
+    for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+        const int buf = (tile - tile_lo) & 1;
+        cp_async_wait_all();
+        __syncthreads();
+        if (tile < tile_hi) load_tile(tile + 1, buf ^ 1);
+        const bf16* kt = ks + (size_t)buf * kKeys * DS;
+
+        float sc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[nt][i] = 0.0f;
+        for (int kk = 0; kk < D; kk += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a, qs + (size_t)(warp * 16 + (lane & 15)) * DS + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int pair = 0; pair < 2; ++pair) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kt + (size_t)(pair * 16 + ((lane >> 4) & 1) * 8 + (lane & 7)) * DS + kk + ((lane >> 3) & 1) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma_bf16(sc[2 * pair], a, b0);
+                mma_bf16(sc[2 * pair + 1], a, b1);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = tile * kKeys + nt * 8 + 2 * t4 + e;
+                    const bool seen = live[half] && j >= lo_row[half] && j <= p_row[half];
+                    const float v = seen ? sc[nt][2 * half + e] * scale_log2 : -CUDART_INF_F;
+                    sc[nt][2 * half + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[half], mx);
+            const bool none = m_new == -CUDART_INF_F;
+            corr[half] = none ? 1.0f : exp2f(m_run[half] - m_new);
+            float sum = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float p = none ? 0.0f : exp2f(sc[nt][2 * half + e] - m_new);
+                    sc[nt][2 * half + e] = p;
+                    sum += p;
+                }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run[half] = l_run[half] * corr[half] + sum;
+            m_run[half] = m_new;
+        }
+#pragma unroll
+        for (int nt = 0; nt < N8; ++nt) {
+            o[nt][0] *= corr[0];
+            o[nt][1] *= corr[0];
+            o[nt][2] *= corr[1];
+            o[nt][3] *= corr[1];
+        }
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) {
+            const uint32_t a[4] = {pack_bf16(sc[2 * k2][0], sc[2 * k2][1]), pack_bf16(sc[2 * k2][2], sc[2 * k2][3]),
+                                   pack_bf16(sc[2 * k2 + 1][0], sc[2 * k2 + 1][1]), pack_bf16(sc[2 * k2 + 1][2], sc[2 * k2 + 1][3])};
+#pragma unroll
+            for (int np = 0; np < N8 / 2; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, kt + (size_t)(k2 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * DS + np * 16 + ((lane >> 4) & 1) * 8);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+                mma_bf16(o[2 * np], a, b0);
+                mma_bf16(o[2 * np + 1], a, b1);
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = warp * 16 + g + 8 * half, tok = row / HB, head = hg * HB + row % HB;
+        if (tok >= n_here || head >= n_head) continue;
+        const float inv = 1.0f / l_run[half];
+        float* dst = out + (size_t)(first + tok) * ldo + (size_t)head * RANK + 2 * t4;
+#pragma unroll
+        for (int nt = 0; nt < N8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+    }
+}
+
+template <int N8>
+int launch_rows(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table, int table_stride,
+                float* out, int64_t ldo, int n_seq, int max_q_len, int n_head, int rot, int page_size, float scale, int window, cudaStream_t s) {
+    // Up to sixteen heads of a token side by side (more heads: groups of equal size), then the next tokens.
+    const int groups = (n_head + 15) / 16, HB = (n_head + groups - 1) / groups, TOK = 64 / HB, DS = 8 * N8 + rot + 8;
+    const size_t smem = (size_t)(64 + 2 * kKeys) * DS * sizeof(bf16);
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_rows_kernel<N8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, (n_head + HB - 1) / HB);
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_rows_kernel<N8>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start, n_past,
+                                       block_table, table_stride, out, ldo, n_head, rot, page_size, scale * 1.4426950408889634f, window, HB));
+    return LB_OK;
 }
 
 // out[t, h, :] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the parts, in their order.
@@ -262,6 +441,75 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
+// C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n]: the products per head around the attention
+// (the keys' maps moved onto the queries; the values' maps on the attended latents) on the tensor cores.  A is float (rounded to
+// bfloat16 as it is staged), B and C bfloat16.  A block makes 64 rows x 64 columns of one head, a warp 16 of the rows; K in chunks of 32.
+// KN: B's rows run along n (b_n = 1), else along k (b_k = 1).  KC: K in chunks of that many (32; 128 for steps of few rows, whose
+// blocks then make fewer round trips to memory).
+template <bool KN, int KC>
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(const float* __restrict__ A, int64_t lda, int64_t a_head, const bf16* __restrict__ B, int64_t b_head, int64_t b_k, int64_t b_n,
+                       bf16* __restrict__ C, int64_t ldc, int64_t c_head, int M, int N, int K) {
+    __shared__ __align__(16) bf16 As[64][KC + 8];
+    __shared__ __align__(16) bf16 Bs[KN ? KC : 64][KN ? 72 : KC + 8];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const float* a = A + (size_t)h * a_head;
+    const bf16* b = B + (size_t)h * b_head;
+    float acc[8][4] = {};
+    for (int k0 = 0; k0 < K; k0 += KC) {
+        for (int idx = threadIdx.x; idx < 64 * (KC / 4); idx += 128) {      // 64 rows x groups of four values
+            const int r = idx / (KC / 4), k = (idx % (KC / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m0 + r < M && k0 + k < K) v = *reinterpret_cast<const float4*>(a + (size_t)(m0 + r) * lda + k0 + k);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<uint2*>(&As[r][k]) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+        if (KN) {
+            for (int idx = threadIdx.x; idx < KC * 8; idx += 128) {         // k rows x 8 pieces of eight n
+                const int k = idx >> 3, n = (idx & 7) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (k0 + k < K && n0 + n < N) v = *reinterpret_cast<const uint4*>(b + (size_t)(k0 + k) * b_k + n0 + n);
+                *reinterpret_cast<uint4*>(&Bs[k][n]) = v;
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < 64 * (KC / 8); idx += 128) {  // 64 n rows x pieces of eight k
+                const int n = idx / (KC / 8), k = (idx % (KC / 8)) * 8;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + n < N && k0 + k < K) v = *reinterpret_cast<const uint4*>(b + (size_t)(n0 + n) * b_n + k0 + k);
+                *reinterpret_cast<uint4*>(&Bs[n][k]) = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < KC; kk += 16) {
+            if (k0 + kk >= K) break;
+            uint32_t af[4];
+            ldmatrix_x4(af, &As[warp * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                uint32_t bfr[2];
+                if (KN) ldmatrix_x2_trans(bfr, &Bs[kk + (lane & 15)][nt * 8]);
+                else ldmatrix_x2(bfr, &Bs[nt * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+                mma_bf16(acc[nt], af, bfr);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = m0 + warp * 16 + g + 8 * half;
+        if (r >= M) continue;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int n = n0 + nt * 8 + 2 * t4;
+            if (n < N) *reinterpret_cast<__nv_bfloat162*>(C + (size_t)r * ldc + (size_t)h * c_head + n) = __floats2bfloat162_rn(acc[nt][2 * half], acc[nt][2 * half + 1]);
+        }
+    }
+}
+
 size_t mma_smem_bytes(int m, int rank, int rot) {
     const int DS = rank + rot + 8;
     return ((size_t)m * DS + (size_t)2 * kKeys * DS + (size_t)m * kPStride) * sizeof(bf16) + (size_t)8 * m * sizeof(float);
@@ -270,18 +518,16 @@ size_t mma_smem_bytes(int m, int rank, int rot) {
 template <int MT, int RT>
 int launch_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, int n_head, int rot,
-               int page_size, float scale, int window, int n_splits, cudaStream_t s) {
+               int page_size, float scale, int window, int n_splits, bool merge_parts, cudaStream_t s) {
     constexpr int M = 16 * MT;
-    int hb_log2 = 0;
-    while ((1 << hb_log2) < n_head && (1 << hb_log2) < M) ++hb_log2;
-    const int HB = 1 << hb_log2, TOK = M / HB;
+    const int groups = (n_head + 15) / 16, HB = (n_head + groups - 1) / groups, TOK = M / HB;
     const size_t smem = mma_smem_bytes(M, 32 * RT, rot);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<MT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, ((n_head + HB - 1) / HB) * n_splits);
     LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_mma_kernel<MT, RT>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start,
                                        n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_head, rot, page_size,
-                                       scale * 1.4426950408889634f, window, hb_log2, n_splits));
-    if (n_splits > 1)
+                                       scale * 1.4426950408889634f, window, HB, n_splits));
+    if (n_splits > 1 && merge_parts)            // else the caller merges the parts itself (lb_latent_finish)
         LB_CHECK_CUDA(lb_launch_overlapped(latent_merge_kernel, dim3(n_tokens, n_head), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml, out, ldo,
                                            n_tokens, n_head, 32 * RT, n_splits));
     return LB_OK;
@@ -295,6 +541,35 @@ bool built_rank(int rank) {
 
 }  // namespace
 
+// Everything the 16-byte loads and paired stores need: rows of four floats in A, pieces of eight values along B's rows, pairs in C.
+extern "C" int lb_head_matmul_mma_supports(int64_t lda, int64_t a_head, int64_t b_head, int64_t b_k, int64_t b_n, int64_t ldc, int64_t c_head, int N, int K) {
+    const bool kn = b_n == 1;
+    if (!kn && b_k != 1) return 0;
+    return lda % 4 == 0 && a_head % 4 == 0 && K % 4 == 0 && b_head % 8 == 0 && (kn ? b_k % 8 == 0 && N % 8 == 0 : b_n % 8 == 0 && K % 8 == 0) && ldc % 2 == 0 &&
+                   c_head % 2 == 0 && N % 2 == 0 ? 1 : 0;
+}
+
+extern "C" int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
+                                  int64_t c_head, int M, int N, int K, int n_head, void* stream) {
+    if (!lb_head_matmul_mma_supports(lda, a_head, b_head, b_k, b_n, ldc, c_head, N, K))
+        return lb_fail(LB_ERR_UNSUPPORTED, "product per head on tensor cores: strides or sizes off its 16-byte pieces");
+    LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && n_head > 0 && n_head <= 65535, "product per head: bad sizes M=%d N=%d K=%d heads=%d", M, N, K, n_head);
+    if (M == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const dim3 grid((N + 63) / 64, (M + 63) / 64, n_head);
+#define LB_HEADS(KN, KC) LB_CHECK_CUDA(lb_launch_overlapped(head_matmul_mma_kernel<KN, KC>, grid, dim3(128), 0, s, A, lda, a_head, (const bf16*)B, b_head, b_k, \
+                                                            b_n, (bf16*)C, ldc, c_head, M, N, K))
+    if (b_n == 1) {
+        if (M <= 64) LB_HEADS(true, 128);
+        else LB_HEADS(true, 32);
+    } else {
+        if (M <= 64) LB_HEADS(false, 128);
+        else LB_HEADS(false, 32);
+    }
+#undef LB_HEADS
+    return LB_OK;
+}
+
 extern "C" int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size) {
     return n_head > 0 && built_rank(rank) && rot >= 0 && rot % 16 == 0 && page_size > 0 && mma_smem_bytes(32, rank, rot) <= 200 * 1024 ? 1 : 0;
 }
@@ -302,17 +577,25 @@ extern "C" int lb_latent_attention_mma_supports(int n_head, int rank, int rot, i
 extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
                                        const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
                                        int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
-                                       int n_splits, void* stream) {
+                                       int n_splits, int merge_parts, void* stream) {
     if (!lb_latent_attention_mma_supports(n_head, rank, rot, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "latent attention on tensor cores: rank %d, rot %d are not built", rank, rot);
-    LB_CHECK_ARG(n_tokens >= 0 && n_seq >= 0 && max_q_len >= 0 && n_splits >= 1 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+    LB_CHECK_ARG(n_tokens >= 0 && n_seq >= 0 && max_q_len >= 0 && n_splits >= 1 && out != nullptr && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                  "latent attention: bad sizes tokens=%d requests=%d splits=%d", n_tokens, n_seq, n_splits);
     if (n_tokens == 0 || n_seq == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
-    // Two 16-row tiles a block where a request brings several tokens and the sums still fit the registers; one otherwise.
+    // Runs of tokens with a latent of up to 256 values: 64 rows a block, every warp with rows of its own.
+    if (max_q_len > 1 && n_splits == 1 && rank <= 256 && (size_t)(64 + 2 * kKeys) * (rank + rot + 8) * sizeof(bf16) <= 200 * 1024) {
+#define LB_ROWS(N8) \
+    if (rank == 8 * N8) return launch_rows<N8>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, n_seq, max_q_len, n_head, rot, page_size, \
+                                               scale, window, s)
+        LB_ROWS(4); LB_ROWS(8); LB_ROWS(12); LB_ROWS(16); LB_ROWS(24); LB_ROWS(32);
+#undef LB_ROWS
+    }
+    // Else two 16-row tiles a block where a request brings several tokens and the sums still fit the registers; one otherwise.
     const bool two = max_q_len > 1 && rank <= 256;
 #define LB_MMA(MT, RT) return launch_mma<MT, RT>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_seq, \
-                                                 max_q_len, n_head, rot, page_size, scale, window, n_splits, s)
+                                                 max_q_len, n_head, rot, page_size, scale, window, n_splits, merge_parts != 0, s)
 #define LB_MMA_RANK(RT)            \
     if (rank == 32 * RT) {         \
         if (two) LB_MMA(2, RT);    \

@@ -105,105 +105,126 @@ __global__ void shift_keep_kernel(const T* __restrict__ h, int64_t ldh, T* __res
 // z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2, with a = softplus(p) and b = 1/2 + softplus(q).
 __device__ __forceinline__ float softplus(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
 
-template <typename T>
+__device__ __forceinline__ float xielu_of(float v, float a, float b) { return v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v); }
+
+// VEC: rows start on 16-byte boundaries and hold a multiple of a 16-byte piece, so a thread takes a piece at a time.
+template <typename T, bool VEC>
 __global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int cols, const float* __restrict__ pq) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const float a = softplus(pq[0]), b = 0.5f + softplus(pq[1]);
     T* row = z + (size_t)blockIdx.x * ldz;
-    for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) {
-        const float v = lb_to_float(row[i]);
-        const float r = v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v);
-        row[i] = lb_from_float<T>(r);
+    if (VEC) {
+        constexpr int N = 16 / sizeof(T);
+        for (int i = (threadIdx.x + blockIdx.y * blockDim.x) * N; i < cols; i += blockDim.x * gridDim.y * N) {
+            uint4 raw = *reinterpret_cast<uint4*>(row + i);
+            T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int k = 0; k < N; ++k) v[k] = lb_from_float<T>(xielu_of(lb_to_float(v[k]), a, b));
+            *reinterpret_cast<uint4*>(row + i) = raw;
+        }
+    } else {
+        for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) row[i] = lb_from_float<T>(xielu_of(lb_to_float(row[i]), a, b));
     }
 }
 
 // ---------------------------------------------------------------- gated per-token side input
-// For NT consecutive tokens a block makes g = gelu_tanh(G x) * e (e: the token's row of the side table), y = P g
-// and x += y / sqrt(mean(y^2) + eps) * w.  G is [dim, width], P is [width, dim]; the rows of x are 32-bit and stay so.
-// The weights are read once per block, whatever NT.
-template <typename T, int NT>
+// g = gelu_tanh(G x) * e (e: the token's row of the side table), y = P g, x += y / sqrt(mean(y^2) + eps) * w, with G [dim, width]
+// and P [width, dim]; the rows of x are 32-bit and stay so.  Two launches: the gate spread over (token, eight features) blocks, a warp
+// per feature with lanes along the width; then a block per token, a thread per output column with P's short row in order.  Every sum's
+// order depends on the sizes only.
+template <typename T>
 __global__ void __launch_bounds__(256)
-token_side_kernel(float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ tokens, const T* __restrict__ table, const T* __restrict__ G,
-                  const T* __restrict__ P, const float* __restrict__ w, int n_tokens, int width, int dim, float eps) {
-    extern __shared__ float sm[];              // x rows [NT][width], then y rows [NT][width], then g [NT][dim], then sums
-    float* xs = sm;
-    float* ys = xs + (size_t)NT * width;
-    float* gs = ys + (size_t)NT * width;
-    float* red = gs + (size_t)NT * dim;        // [NT][8 warps] + [NT]
+side_gate_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ tokens, const T* __restrict__ table, const T* __restrict__ G,
+                 float* __restrict__ g, int width, int dim) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
-    const int t0 = blockIdx.x * NT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nt = min(NT, n_tokens - t0);
-    for (int i = threadIdx.x; i < NT * width; i += blockDim.x) {
-        const int u = i / width, c = i - u * width;
-        xs[i] = u < nt ? x[(size_t)(t0 + u) * ldx + c] : 0.0f;
-    }
-    __syncthreads();
-    // g: a warp per gate feature, lanes along the width.
-    for (int d = warp; d < dim; d += 8) {
-        const T* row = G + (size_t)d * width;
-        float acc[NT];
-#pragma unroll
-        for (int u = 0; u < NT; ++u) acc[u] = 0.0f;
-        for (int c = lane; c < width; c += 32) {
-            const float gv = lb_to_float(row[c]);
-#pragma unroll
-            for (int u = 0; u < NT; ++u) acc[u] = fmaf(gv, xs[u * width + c], acc[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < NT; ++u) {
-            const float v = lb_warp_sum(acc[u]);
-            if (lane == 0 && u < nt) gs[u * dim + d] = lb_gelu_tanh(v) * lb_to_float(table[(size_t)tokens[t0 + u] * dim + d]);
-        }
-    }
-    __syncthreads();
-    // y: a thread per output column, the short row of P in order.
-    float ss[NT];
-#pragma unroll
-    for (int u = 0; u < NT; ++u) ss[u] = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const T* row = P + (size_t)c * dim;
-        float acc[NT];
-#pragma unroll
-        for (int u = 0; u < NT; ++u) acc[u] = 0.0f;
-        for (int d = 0; d < dim; ++d) {
-            const float pv = lb_to_float(row[d]);
-#pragma unroll
-            for (int u = 0; u < NT; ++u) acc[u] = fmaf(pv, gs[u * dim + d], acc[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < NT; ++u) {
-            ys[u * width + c] = acc[u];
-            ss[u] = fmaf(acc[u], acc[u], ss[u]);
-        }
-    }
-#pragma unroll
-    for (int u = 0; u < NT; ++u) {
-        const float v = lb_warp_sum(ss[u]);
-        if (lane == 0) red[u * 8 + warp] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x < NT) {
-        float total = 0.0f;
-        for (int k = 0; k < 8; ++k) total += red[threadIdx.x * 8 + k];
-        red[NT * 8 + threadIdx.x] = 1.0f / sqrtf(total / (float)width + eps);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < nt * width; i += blockDim.x) {
-        const int u = i / width, c = i - u * width;
-        x[(size_t)(t0 + u) * ldx + c] = xs[i] + ys[i] * red[NT * 8 + u] * w[c];
-    }
+    const int t = blockIdx.x, d = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (d >= dim) return;
+    const T* row = G + (size_t)d * width;
+    const float* xr = x + (size_t)t * ldx;
+    float acc = 0.0f;
+    for (int c = lane; c < width; c += 32) acc = fmaf(lb_to_float(row[c]), xr[c], acc);
+    acc = lb_warp_sum(acc);
+    if (lane == 0) g[(size_t)t * dim + d] = lb_gelu_tanh(acc) * lb_to_float(table[(size_t)tokens[t] * dim + d]);
 }
 
-template <typename T, int NT>
-int launch_token_side(float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* G, const void* P, const float* w,
+template <typename T>
+__global__ void __launch_bounds__(256)
+side_proj_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ g, const T* __restrict__ P, const float* __restrict__ w, int width, int dim,
+                 float eps) {
+    extern __shared__ float sm[];              // g [dim], then y [width]
+    __shared__ float scratch[33];
+    float* gs = sm;
+    float* ys = sm + dim;
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) gs[d] = g[(size_t)t * dim + d];
+    __syncthreads();
+    float ss = 0.0f;
+    constexpr int N = 16 / sizeof(T);
+    const bool pieces = dim % N == 0 && (reinterpret_cast<uintptr_t>(P) & 15) == 0;        // P's rows start on 16-byte boundaries
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const T* row = P + (size_t)c * dim;
+        float acc = 0.0f;
+        if (pieces) {
+            for (int d = 0; d < dim; d += N) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(row + d);
+                const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int k = 0; k < N; ++k) acc = fmaf(lb_to_float(v[k]), gs[d + k], acc);      // the same order as one by one
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) acc = fmaf(lb_to_float(row[d]), gs[d], acc);
+        }
+        ys[c] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    float* xr = x + (size_t)t * ldx;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xr[c] += ys[c] * inv * w[c];
+}
+
+// The pieces around two library products for steps of many tokens (bfloat16).
+__global__ void rows_to_bf16_kernel(const float* __restrict__ x, int64_t ldx, __nv_bfloat16* __restrict__ y, int64_t ldy, int cols) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const float* in = x + (size_t)blockIdx.x * ldx;
+    __nv_bfloat16* out = y + (size_t)blockIdx.x * ldy;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+__global__ void side_gate_finish_kernel(const float* __restrict__ pre, int64_t ldp, const int32_t* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                        __nv_bfloat16* __restrict__ g16, int64_t ldg, int dim) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x)
+        g16[(size_t)t * ldg + d] = __float2bfloat16_rn(lb_gelu_tanh(pre[(size_t)t * ldp + d]) * __bfloat162float(table[(size_t)tokens[t] * dim + d]));
+}
+
+__global__ void rms_add_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const float* __restrict__ w, int width, float eps) {
+    __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const float* yr = y + (size_t)blockIdx.x * ldy;
+    float* xr = x + (size_t)blockIdx.x * ldx;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xr[i] += yr[i] * inv * w[i];
+}
+
+template <typename T>
+int launch_token_side(float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* G, const void* P, const float* w, float* g,
                       int n_tokens, int width, int dim, float eps, cudaStream_t s) {
-    const size_t smem = ((size_t)NT * (2 * width + dim) + NT * 9) * sizeof(float);
+    const size_t smem = (size_t)(width + dim) * sizeof(float);
     if (smem > 200 * 1024) return lb_fail(LB_ERR_UNSUPPORTED, "token side input: rows of %d values with %d gate features do not fit a block", width, dim);
-    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(token_side_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    LB_CHECK_CUDA(lb_launch_overlapped(token_side_kernel<T, NT>, dim3((n_tokens + NT - 1) / NT), dim3(256), smem, s, x, ldx, tokens,
-                                       (const T*)table, (const T*)G, (const T*)P, w, n_tokens, width, dim, eps));
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(side_proj_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LB_CHECK_CUDA(lb_launch_overlapped(side_gate_kernel<T>, dim3(n_tokens, (dim + 7) / 8), dim3(256), 0, s, (const float*)x, ldx, tokens, (const T*)table,
+                                       (const T*)G, g, width, dim));
+    LB_CHECK_CUDA(lb_launch_overlapped(side_proj_kernel<T>, dim3(n_tokens), dim3(256), smem, s, x, ldx, (const float*)g, (const T*)P, w, width, dim, eps));
     return LB_OK;
 }
 
@@ -274,25 +295,48 @@ extern "C" int lb_xielu(int dtype, void* z, int64_t ldz, int n_rows, int cols, c
     LB_CHECK_ARG(n_rows >= 0 && cols > 0 && pq != nullptr, "xielu: bad sizes n_rows=%d cols=%d", n_rows, cols);
     if (n_rows == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
-    const dim3 grid(n_rows, (cols + 2047) / 2048);
-    if (dtype == LB_F32) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
-    else if (dtype == LB_BF16) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
-    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "xielu: unknown dtype %d", dtype);
+    const int piece = dtype == LB_F32 ? 4 : 8;
+    const bool vec = cols % piece == 0 && ldz % piece == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+    const dim3 grid(n_rows, vec ? (cols / piece + 255) / 256 : (cols + 2047) / 2048);
+    if (dtype == LB_F32) {
+        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, true>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
+        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, false>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
+    } else if (dtype == LB_BF16) {
+        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
+        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
+    } else return lb_fail(LB_ERR_INVALID_ARGUMENT, "xielu: unknown dtype %d", dtype);
     return LB_OK;
 }
 
 extern "C" int lb_token_side(int dtype, float* x, int64_t ldx, const int32_t* tokens, const void* table, const void* gate, const void* proj,
-                             const float* weight, int n_tokens, int width, int dim, float eps, void* stream) {
-    LB_CHECK_ARG(n_tokens >= 0 && width > 0 && dim > 0, "token side input: bad sizes n_tokens=%d width=%d dim=%d", n_tokens, width, dim);
+                             const float* weight, float* g, int n_tokens, int width, int dim, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0 && dim > 0 && g != nullptr, "token side input: bad sizes n_tokens=%d width=%d dim=%d", n_tokens, width, dim);
     if (n_tokens == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
-    // Few tokens: a block each, so that the step spreads over the GPU; many: eight a block share one pass over the weights.
-    const bool many = n_tokens > 64 && ((size_t)8 * (2 * width + dim) + 72) * sizeof(float) <= 200 * 1024;
-    if (dtype == LB_F32)
-        return many ? launch_token_side<float, 8>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s)
-                    : launch_token_side<float, 1>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s);
-    if (dtype == LB_BF16)
-        return many ? launch_token_side<__nv_bfloat16, 8>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s)
-                    : launch_token_side<__nv_bfloat16, 1>(x, ldx, tokens, table, gate, proj, weight, n_tokens, width, dim, eps, s);
+    if (dtype == LB_F32) return launch_token_side<float>(x, ldx, tokens, table, gate, proj, weight, g, n_tokens, width, dim, eps, s);
+    if (dtype == LB_BF16) return launch_token_side<__nv_bfloat16>(x, ldx, tokens, table, gate, proj, weight, g, n_tokens, width, dim, eps, s);
     return lb_fail(LB_ERR_INVALID_ARGUMENT, "token side input: unknown dtype %d", dtype);
+}
+
+extern "C" int lb_rows_to_bf16(const float* x, int64_t ldx, void* y, int64_t ldy, int n_rows, int cols, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && cols > 0, "rows to bfloat16: bad sizes rows=%d cols=%d", n_rows, cols);
+    if (n_rows == 0) return LB_OK;
+    LB_CHECK_CUDA(lb_launch_overlapped(rows_to_bf16_kernel, dim3(n_rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ldx, (__nv_bfloat16*)y, ldy, cols));
+    return LB_OK;
+}
+
+extern "C" int lb_side_gate_finish(const float* pre, int64_t ldp, const int32_t* tokens, const void* table, void* g16, int64_t ldg, int n_tokens, int dim,
+                                   void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && dim > 0, "token side input: bad sizes n_tokens=%d dim=%d", n_tokens, dim);
+    if (n_tokens == 0) return LB_OK;
+    LB_CHECK_CUDA(lb_launch_overlapped(side_gate_finish_kernel, dim3(n_tokens), dim3(dim >= 256 ? 256 : dim > 64 ? 128 : 64), 0, static_cast<cudaStream_t>(stream), pre,
+                                       ldp, tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)g16, ldg, dim));
+    return LB_OK;
+}
+
+extern "C" int lb_rms_add(float* x, int64_t ldx, const float* y, int64_t ldy, const float* weight, int n_rows, int width, float eps, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && width > 0, "rms add: bad sizes rows=%d width=%d", n_rows, width);
+    if (n_rows == 0) return LB_OK;
+    LB_CHECK_CUDA(lb_launch_overlapped(rms_add_kernel, dim3(n_rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ldx, y, ldy, weight, width, eps));
+    return LB_OK;
 }

@@ -295,14 +295,29 @@ void xielu(cudaStream_t s, const Rows& z, int n_rows, const float* pq) {
     check(lb_xielu(code(z.dtype, "z"), z.data, z.stride, n_rows, static_cast<int>(z.cols), pq, s), "xielu");
 }
 
-void token_side(cudaStream_t s, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
+void token_side(const Runtime& rt, Workspace* ws, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
                 const float* weight, int n_tokens, float eps) {
     const int64_t dim = gate.dim(0), width = gate.dim(1);
     if (x.dtype != DType::F32 || x.cols != width || proj.dim(0) != width || proj.dim(1) != dim || table.dim(1) != dim || gate.dtype != proj.dtype ||
         gate.dtype != table.dtype)
         throw invalid_argument("token side input: tensors do not fit");
-    check(lb_token_side(code(gate.dtype, "gate"), x.f32(), x.stride, tokens, table.data, gate.data, proj.data, weight, n_tokens, static_cast<int>(width),
-                        static_cast<int>(dim), eps, s), "token_side");
+    cudaStream_t s = rt.stream;
+    if (gate.dtype == DType::BF16 && n_tokens > 64 && width % 8 == 0 && dim % 8 == 0) {
+        const Rows x16 = ws->get("side.x16", n_tokens, width, DType::BF16);
+        check(lb_rows_to_bf16(x.f32(), x.stride, x16.data, x16.stride, n_tokens, static_cast<int>(width), s), "rows_to_bf16");
+        const Rows pre = ws->get("side.pre", n_tokens, dim, DType::F32);
+        linear(rt, ws, x16, gate, nullptr, pre, n_tokens, kNone, nullptr);
+        const Rows g16 = ws->get("side.g16", n_tokens, dim, DType::BF16);
+        check(lb_side_gate_finish(pre.f32(), pre.stride, tokens, table.data, g16.data, g16.stride, n_tokens, static_cast<int>(dim), s), "side_gate_finish");
+        const Rows y = ws->get("side.y", n_tokens, width, DType::F32);
+        linear(rt, ws, g16, proj, nullptr, y, n_tokens, kNone, nullptr);
+        check(lb_rms_add(x.f32(), x.stride, y.f32(), y.stride, weight, n_tokens, static_cast<int>(width), eps, s), "rms_add");
+        return;
+    }
+    const Rows g = ws->get("side.g", n_tokens, dim, DType::F32);
+    check(lb_token_side(code(gate.dtype, "gate"), x.f32(), x.stride, tokens, table.data, gate.data, proj.data, weight, g.f32(), n_tokens,
+                        static_cast<int>(width), static_cast<int>(dim), eps, s), "token_side");
+    launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float* freq, const int32_t* positions, const int32_t* slot_mapping,
@@ -321,8 +336,29 @@ void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t*
 
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
                  int64_t c_head, int m, int n, int k, int n_head) {
+    if (a.dtype == DType::F32 && b.dtype == DType::BF16 && c.dtype == DType::BF16 &&
+        lb_head_matmul_mma_supports(a.stride, a_head, b_head, b_k, b_n, c.stride, c_head, n, k)) {
+        check(lb_head_matmul_mma(a.f32(), a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride, c_head, m, n, k, n_head, s), "head_matmul_mma");
+        return;
+    }
     check(lb_head_matmul(code(a.dtype, "a"), code(b.dtype, "b"), code(c.dtype, "c"), a.data, a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride,
                          c_head, m, n, k, n_head, s), "head_matmul");
+}
+
+bool latent_few_supports(const LatentShape& a) { return lb_latent_few_supports(a.dim, a.rot, a.rank, a.vdim, 1) != 0; }
+
+void latent_prepare(cudaStream_t s, const Rows& qd, const Tensor& uk, const float* gain, const float* freq, const int32_t* positions,
+                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps) {
+    if (qd.dtype != DType::F32 || uk.dtype != DType::BF16 || wide.dtype != DType::BF16) throw invalid_argument("latent queries: float32 rows, bfloat16 map and wide queries");
+    check(lb_latent_prepare(qd.f32(), qd.stride, uk.data, gain, freq, positions, slot_mapping, cache, wide.data, wide.stride, n_tokens, a.n_head, a.dim, a.rot,
+                            a.rot_dims, a.rank, eps, s), "latent_prepare");
+}
+
+void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, const float* part_ml, const Tensor& uv, const Rows& values, int n_tokens,
+                   const LatentShape& a, int n_splits) {
+    if (attended.dtype != DType::F32 || uv.dtype != DType::BF16 || values.dtype != DType::BF16) throw invalid_argument("latent values: float32 latents, bfloat16 map and values");
+    check(lb_latent_finish(attended.f32(), attended.stride, part_o, part_ml, uv.data, values.data, values.stride, n_tokens, a.n_head, a.rank, a.vdim, n_splits, s),
+          "latent_finish");
 }
 
 bool latent_mma_supports(const LatentShape& a) { return lb_latent_attention_mma_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }
@@ -335,11 +371,11 @@ int latent_splits(int n_seq, int n_head, int span) {
 
 void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                           int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
-                          int n_splits) {
+                          int n_splits, bool merge) {
     if (wide.dtype != DType::BF16 || out.dtype != DType::F32) throw invalid_argument("latent attention on tensor cores: bfloat16 wide queries, float32 attended latents");
-    check(lb_latent_attention_mma(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.f32(), out.stride, part_o, part_ml, n_tokens,
-                                  n_seq, max_q_len, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, n_splits, s), "latent_attention_mma");
-    if (n_splits > 1) launches.fetch_add(1, std::memory_order_relaxed);
+    check(lb_latent_attention_mma(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.f32(), out.stride, part_o, part_ml, n_tokens, n_seq,
+                                  max_q_len, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, n_splits, merge ? 1 : 0, s), "latent_attention_mma");
+    if (n_splits > 1 && merge) launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,

@@ -116,7 +116,9 @@ void rms_shift(cudaStream_t s, const Rows& x, const float* weight, const float* 
 // In place over z[:n_rows]: the xIELU with its two learned numbers pq (float, on the device).
 void xielu(cudaStream_t s, const Rows& z, int n_rows, const float* pq);
 // x[t] += rms(proj (gelu_tanh(gate x[t]) * table[tokens[t]])) * weight.
-void token_side(cudaStream_t s, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
+// Steps of more than 64 tokens in bfloat16 run the two maps as library products (x rounded to bfloat16 first); all others as two
+// kernels of their own with 32-bit rows.  `ws` lends the scratch.
+void token_side(const Runtime& rt, Workspace* ws, const Rows& x, const int32_t* tokens, const Tensor& table, const Tensor& gate, const Tensor& proj,
                 const float* weight, int n_tokens, float eps);
 
 // ---- attention over a cache of latent rows [c (rank) | r (rot)] ----
@@ -129,15 +131,22 @@ void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float*
                   void* cache, DType cache_dtype, int n_tokens, const LatentShape& a, float eps);
 void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t* positions, const Rows& wide, int n_tokens, const LatentShape& a);
 // C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n].
+// Float rows, bfloat16 maps and output whose strides fit 16-byte pieces go to the tensor cores; everything else to the 32-bit units.
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
                  int64_t c_head, int m, int n, int k, int n_head);
+// Steps of few tokens in bfloat16: rotation, keys' map and cache row in one launch; merge of the attention's parts and values' map in one.
+bool latent_few_supports(const LatentShape& a);
+void latent_prepare(cudaStream_t s, const Rows& qd, const Tensor& uk, const float* gain, const float* freq, const int32_t* positions,
+                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps);
+void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, const float* part_ml, const Tensor& uv, const Rows& values, int n_tokens,
+                   const LatentShape& a, int n_splits);
 // The tensor-core kernel (bfloat16 wide queries and cache): whether it takes the shape, into how many parts a decode step's keys are cut
 // (a function of the step's shape and the longest span a query can see, so a recorded step and an eager one cut alike), and the launch.
 bool latent_mma_supports(const LatentShape& a);
 int latent_splits(int n_seq, int n_head, int span);
 void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                           int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
-                          int n_splits);
+                          int n_splits, bool merge = true);       // merge false: the parts are left for latent_finish
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
                       const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a);
 

@@ -132,18 +132,26 @@ public:
         // Queries (and this step's cache rows) in 32-bit: the norm of the latent and both rotations read them.
         const Rows qd = ws.get(own_latent ? "latent.qd" : "latent.q", T, q_cols + (own_latent ? D : 0), DType::F32);
         proj.forward(ctx, h, qd, T);
-        if (own_latent) kernels::latent_store(s, qd.columns(q_cols, D), latent_gain, freq, ctx.positions, view->slot_mapping, cache, dt, T, shape, eps);
         const Rows q = qd.columns(0, q_cols);
         // bfloat16 and a shape the tensor-core kernel takes: wide queries in bfloat16 for it; else 32-bit throughout.
         const bool tensor = dt == DType::BF16 && kernels::latent_mma_supports(shape);
+        // Steps of few tokens are bound by their launches: one launch before the attention, one after it.
+        const bool few = tensor && T <= kFewTokens && kernels::latent_few_supports(shape);
         const Rows wide = ws.get(tensor ? "latent.wide16" : "latent.wide", T, static_cast<int64_t>(a.n_head) * D, tensor ? DType::BF16 : DType::F32);
-        kernels::rope_heads(s, q, freq, ctx.positions, wide, T, shape);
-        if (a.dim > 0)
-            kernels::head_matmul(s, q, a.dim + a.rot, uk, static_cast<int64_t>(a.dim) * a.rank, a.rank, 1, wide, D, T, a.rank, a.dim, a.n_head);
-        else
-            LIYAB_CUDA(cudaMemset2DAsync(wide.data, static_cast<size_t>(wide.stride) * 4, 0, static_cast<size_t>(wide.cols) * 4, static_cast<size_t>(T), s));
+        if (few) {
+            kernels::latent_prepare(s, qd, uk, latent_gain, freq, ctx.positions, view->slot_mapping, own_latent ? cache : nullptr, wide, T, shape, eps);
+        } else {
+            if (own_latent) kernels::latent_store(s, qd.columns(q_cols, D), latent_gain, freq, ctx.positions, view->slot_mapping, cache, dt, T, shape, eps);
+            kernels::rope_heads(s, q, freq, ctx.positions, wide, T, shape);
+            if (a.dim > 0)
+                kernels::head_matmul(s, q, a.dim + a.rot, uk, static_cast<int64_t>(a.dim) * a.rank, a.rank, 1, wide, D, T, a.rank, a.dim, a.n_head);
+            else
+                LIYAB_CUDA(cudaMemset2DAsync(wide.data, static_cast<size_t>(wide.stride) * dtype_size(wide.dtype), 0, static_cast<size_t>(wide.cols) * dtype_size(wide.dtype),
+                                             static_cast<size_t>(T), s));
+        }
         ctx.tap("latent.wide", wide);
         const Rows attended = ws.get("latent.attended", T, static_cast<int64_t>(a.n_head) * a.rank, DType::F32);
+        const Rows values = ws.get("latent.values", T, static_cast<int64_t>(a.n_head) * a.vdim, dt);
         if (tensor) {
             // A decode step's keys are cut over several blocks so that a few requests still fill the GPU.
             const int span = a.window > 0 ? std::min(a.window, ctx.max_positions) : ctx.max_positions;
@@ -154,16 +162,17 @@ public:
                 part_ml = static_cast<float*>(ws.flat("latent.part_ml", static_cast<int64_t>(splits) * T * a.n_head * 2, DType::F32));
             }
             kernels::latent_attention_mma(s, wide, cache, ctx.q_start, ctx.n_past, view->block_table, view->table_width, attended, part_o, part_ml, T,
-                                          ctx.n_seq, ctx.max_q_len, shape, splits);
+                                          ctx.n_seq, ctx.max_q_len, shape, splits, !few);
+            if (few) kernels::latent_finish(s, attended, part_o, part_ml, uv, values, T, shape, splits);
         } else {
             kernels::latent_attention(s, dt, wide, cache, ctx.tok_seq, ctx.positions, view->block_table, view->table_width, attended, T, shape);
         }
-        const Rows values = ws.get("latent.values", T, static_cast<int64_t>(a.n_head) * a.vdim, dt);
-        kernels::head_matmul(s, attended, a.rank, uv, static_cast<int64_t>(a.vdim) * a.rank, 1, a.rank, values, a.vdim, T, a.vdim, a.rank, a.n_head);
+        if (!few) kernels::head_matmul(s, attended, a.rank, uv, static_cast<int64_t>(a.vdim) * a.rank, 1, a.rank, values, a.vdim, T, a.vdim, a.rank, a.n_head);
         ctx.tap("attention", values);
         out.forward(ctx, values, x, T, kernels::kNone, &x);
     }
 
+    static constexpr int kFewTokens = 64;
     kernels::LatentShape a;
     int64_t hidden = 0, q_cols = 0;
     float eps = 1e-6f;
@@ -190,7 +199,7 @@ private:
 
 // ---- gated per-token side input ------------------------------------------------------------------------
 // From a side table with `dim` values per token id: g = gelu_tanh(gate x) * table[token]; y = proj g;
-// x += y / sqrt(mean(y^2) + eps) * gain.  One kernel: the two maps are `dim` wide, far narrower than the stream.
+// x += y / sqrt(mean(y^2) + eps) * gain.  The two maps are `dim` wide, far narrower than the stream.
 
 class GatedTokenSide final : public TokenInput {
 public:
@@ -209,7 +218,7 @@ public:
     }
     bool capturable() const override { return true; }
     void forward(StepContext& ctx, const Rows& x) override {
-        kernels::token_side(ctx.stream(), x, ctx.tokens, table, gate, proj, gain, ctx.n_tokens, eps);
+        kernels::token_side(ctx.runtime, ctx.workspace, x, ctx.tokens, table, gate, proj, gain, ctx.n_tokens, eps);
     }
     float eps;
     Tensor table, gate, proj;
