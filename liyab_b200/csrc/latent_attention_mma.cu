@@ -325,6 +325,7 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) sc[nt][i] = 0.0f;
+#pragma unroll 4
         for (int kk = 0; kk < D; kk += 16) {
             uint32_t a[4];
             ldmatrix_x4(a, qs + (size_t)(warp * 16 + (lane & 15)) * DS + kk + (lane >> 4) * 8);

@@ -253,3 +253,34 @@ def test_greedy_generation_through_the_engine(graphs, models):
                 break
             assert tok == int(np.argmax(row))
             seq.append(tok)
+
+
+def test_command_line_and_sampling(models):
+    """The command line generates greedily what the plain model would, shows the phases with --phases, and the
+    engine's sampler with a seed gives the same tokens twice and other tokens with another seed."""
+    import json
+    from liyab_b200.engine import Engine
+    from liyab_b200.sampling import SamplingParams
+    path, config, weights = models["T"]
+    prompt = tokens_of("T", 90, 9)
+    cmd = [os.path.join(ROOT, "bin", "liyab-cli"), "-m", path, "-p", ",".join(map(str, prompt)), "-n", "8", "--temp", "0", "--dtype", "float32",
+           "--ctx", "128", "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    seq = list(prompt)
+    for tok in lines[1]["tokens"]:
+        row = plain.forward(config, weights, seq)[-1]
+        best = np.sort(row)[-2:]
+        if best[1] - best[0] < 1e-3 * np.abs(row).max():
+            break
+        assert tok == int(np.argmax(row))
+        seq.append(tok)
+    proc = subprocess.run(cmd[:-1] + ["--phases"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0 and "decode phases (ms/token): embed" in proc.stderr, proc.stderr[-2000:]
+    draws = []
+    for seed in (5, 5, 6):       # a draw belongs to (seed, request number of the engine, index): fresh engines, the same request number
+        engine = Engine(model=path, dtype="bfloat16", context_length=128, max_requests=4)
+        draws.append(engine.generate_tokens(prompt, SamplingParams(max_tokens=12, temperature=0.9, top_k=20, top_p=0.95, seed=seed)).tokens)
+        engine.close()
+    assert draws[0] == draws[1] and draws[0] != draws[2] and all(0 <= t < config["vocab"] for t in draws[2])
