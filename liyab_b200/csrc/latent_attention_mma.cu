@@ -66,13 +66,14 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
 
     const int TOK = M / HB;                                      // rows beyond TOK * HB stay empty
     const int s = blockIdx.y, split = blockIdx.z % n_splits, hg = blockIdx.z / n_splits;
-    const int first = q_start[s] + blockIdx.x * TOK;
+    const int qt = gridDim.x - 1 - blockIdx.x;                     // a request's last tiles see the most keys: they start first
+    const int first = q_start[s] + qt * TOK;
     const int n_here = min(TOK, q_start[s + 1] - first);
     if (n_here <= 0) return;
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const int p_first = n_past[s] + blockIdx.x * TOK, p_last = p_first + n_here - 1;
+    const int p_first = n_past[s] + qt * TOK, p_last = p_first + n_here - 1;
     const int lo_min = window > 0 ? max(0, p_first - window + 1) : 0;
     const int32_t* table = block_table + (size_t)s * table_stride;
 
@@ -259,13 +260,14 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
     bf16* ks = qs + (size_t)M * DS;                              // [2][kKeys][DS]
     const int TOK = M / HB;                                      // rows beyond TOK * HB stay empty
     const int s = blockIdx.y, hg = blockIdx.z;
-    const int first = q_start[s] + blockIdx.x * TOK;
+    const int qt = gridDim.x - 1 - blockIdx.x;                     // a request's last tiles see the most keys: they start first
+    const int first = q_start[s] + qt * TOK;
     const int n_here = min(TOK, q_start[s + 1] - first);
     if (n_here <= 0) return;
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const int p_first = n_past[s] + blockIdx.x * TOK, p_last = p_first + n_here - 1;
+    const int p_first = n_past[s] + qt * TOK, p_last = p_first + n_here - 1;
     const int lo_min = window > 0 ? max(0, p_first - window + 1) : 0;
     const int32_t* table = block_table + (size_t)s * table_stride;
     const int tile_lo = lo_min / kKeys, tile_hi = p_last / kKeys;
@@ -593,8 +595,8 @@ extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void
         LB_ROWS(4); LB_ROWS(8); LB_ROWS(12); LB_ROWS(16); LB_ROWS(24); LB_ROWS(32);
 #undef LB_ROWS
     }
-    // Else two 16-row tiles a block where a request brings several tokens and the sums still fit the registers; one otherwise.
-    const bool two = max_q_len > 1 && rank <= 256;
+    // Else two 16-row tiles a block where a request brings several tokens; one otherwise.
+    const bool two = max_q_len > 1;
 #define LB_MMA(MT, RT) return launch_mma<MT, RT>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_seq, \
                                                  max_q_len, n_head, rot, page_size, scale, window, n_splits, merge_parts != 0, s)
 #define LB_MMA_RANK(RT)            \
@@ -603,8 +605,7 @@ extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void
         LB_MMA(1, RT);             \
     }
     LB_MMA_RANK(1) LB_MMA_RANK(2) LB_MMA_RANK(3) LB_MMA_RANK(4) LB_MMA_RANK(6) LB_MMA_RANK(8)
-    if (rank == 384) LB_MMA(1, 12);
-    if (rank == 512) LB_MMA(1, 16);
+    LB_MMA_RANK(12) LB_MMA_RANK(16)
 #undef LB_MMA_RANK
 #undef LB_MMA
     return lb_fail(LB_ERR_UNSUPPORTED, "latent attention on tensor cores: rank %d is not built", rank);
