@@ -2,7 +2,7 @@
 
 P differs from layer to layer in every size the design has (heads, head sizes, latent size, window, rotated
 share, feed-forward or none) and has two blocks that read another block's latent rows with windows of their own.
-T has the sizes that the tensor-core attention kernel takes.  Q has one norm group, no side input, no window, a head count that no kernel tile divides and a latent wider than
+T has the sizes that the tensor-core attention kernel takes, U sizes that fit no kernel's pieces.  Q has one norm group, no side input, no window, a head count that no kernel tile divides and a latent wider than
 128.  R keeps three sizes equal to one (a head count, a head size, the side input's width), norm groups of four
 values, and two blocks on one latent whose windows end one before and on a page border.
 """
@@ -52,7 +52,15 @@ CONFIG_T = dict(architecture="Puzutar", vocab=200, width=128, norm=dict(eps=1e-5
     layer(mixer(20, 8, 32, 8, 96, 0, base=1e5), 128),
     layer(mixer(2, 32, 16, 32, 32, 33), 0),
 ])
-CONFIGS = {"P": (CONFIG_P, 11), "Q": (CONFIG_Q, 12), "R": (CONFIG_R, 13), "T": (CONFIG_T, 14)}
+# Sizes that fit no kernel's pieces: a width that is no multiple of 8, five norm groups, seven heads, rotated parts of 8 of which 6
+# turn, a window of one position (a token sees itself only) beside one wider than any prompt, a side input three values wide, and a
+# latent the tensor-core path takes (512 values) behind 64 rotated ones.
+CONFIG_U = dict(architecture="Puzutar", vocab=97, width=100, norm=dict(eps=1e-4, groups=5), token_side=dict(dim=3), layers=[
+    layer(mixer(7, 24, 8, 40, 72, 1, rot_dims=6, base=77.0), 50),
+    layer(mixer(2, 10, 8, 6, 72, 1000, rot_dims=6, base=77.0, kv_from=0), 0),
+    layer(mixer(1, 16, 64, 32, 512, 45, base=1e6), 60),
+])
+CONFIGS = {"P": (CONFIG_P, 11), "Q": (CONFIG_Q, 12), "R": (CONFIG_R, 13), "T": (CONFIG_T, 14), "U": (CONFIG_U, 15)}
 
 
 def to_bf16_values(a):

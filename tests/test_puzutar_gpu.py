@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # float32: largest |engine - plain| on a logit as a fraction of the largest |logit| of the sequence.
 REL_TOL = {"float32": 3e-5}
-LENGTHS = {"P": [150, 70, 33, 21, 7, 2, 1, 45], "Q": [130, 41, 64, 3, 1, 17], "R": [100, 33, 32, 31, 2, 65], "T": [140, 72, 31, 1, 2, 97, 40]}
+LENGTHS = {"P": [150, 70, 33, 21, 7, 2, 1, 45], "Q": [130, 41, 64, 3, 1, 17], "R": [100, 33, 32, 31, 2, 65], "T": [140, 72, 31, 1, 2, 97, 40], "U": [120, 47, 2, 64, 1, 33]}
 
 
 def tokens_of(name, i, n):
