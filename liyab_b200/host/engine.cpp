@@ -64,7 +64,17 @@ Engine::Engine(const EngineConfig& cfg) : config(cfg) {
         const size_t usable = free_bytes > scratch ? free_bytes - scratch : 0;
         num_pages = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(static_cast<double>(usable) * cfg.kv_memory_fraction / static_cast<double>(per_page)))));
     }
-    cache_ = std::make_unique<CacheManager>(kv_needs, state_needs, cfg.page_size, num_pages, cfg.max_requests, model.runtime.dtype, true);
+    // A windowed group never holds more than its window behind every request plus the tokens of one step: its pool is sized by that,
+    // not by whole contexts (pages leave as soon as the window has passed them).
+    std::map<KvNeed, int> pages_per_group;
+    if (cfg.num_pages <= 0)
+        for (const auto& [unit, need] : kv_needs)
+            if (need.window > 0) {
+                const int64_t behind = (std::min<int64_t>(need.window, max_positions) + cfg.page_size - 1) / cfg.page_size + 2;
+                const int64_t enough = static_cast<int64_t>(cfg.max_requests) * behind + (cfg.max_batched_tokens + cfg.page_size - 1) / cfg.page_size;
+                pages_per_group[need] = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(num_pages, enough)));
+            }
+    cache_ = std::make_unique<CacheManager>(kv_needs, state_needs, cfg.page_size, num_pages, cfg.max_requests, model.runtime.dtype, true, pages_per_group);
     StepperOptions so;
     so.max_step_tokens = cfg.max_batched_tokens;
     so.max_logit_rows = cfg.max_requests;

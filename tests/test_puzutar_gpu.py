@@ -243,6 +243,16 @@ def test_greedy_generation_through_the_engine(graphs, models):
     engine = Engine(model=path, dtype="float32", context_length=256, max_requests=4, max_batched_tokens=48, cuda_graphs=graphs)
     results = engine.generate_batch(prompts, SamplingParams(max_tokens=24, temperature=0.0))
     engine.close()
+    if graphs:
+        # Left to itself the engine serves the design's whole span of positions; the windowed units' pools are sized by their
+        # windows and a step's tokens, not by whole contexts, and the tokens are the same.
+        wide = Engine(model=path, dtype="float32", max_requests=4, max_batched_tokens=48, cuda_graphs=False)
+        assert wide.max_positions > 10 ** 5
+        again = wide.generate_batch(prompts, SamplingParams(max_tokens=24, temperature=0.0))
+        pages = wide.stats()["pages_total"]
+        wide.close()
+        assert [r.tokens for r in again] == [r.tokens for r in results]
+        assert pages <= 2 * (4 * (33 // 16 + 3) + 3), pages
     for prompt, res in zip(prompts, results):
         assert res.error is None and len(res.tokens) == 24
         seq = list(prompt)
