@@ -472,3 +472,126 @@ def sample(logits: torch.Tensor, n_rows: int, temperature: torch.Tensor, top_k: 
                           _dev(out_ids, "out_ids", torch.int32), _opt(out_probs, "out_probs", torch.float32),
                           stream_ptr()), "sample")
     return out_ids
+
+
+# ------------------------------------------------------------------ parallel blocks: norm in groups, token shift, xIELU, side input
+
+for _name, _args in {
+    "lb_rms_groups": [_i, _p, _l, _p, _p, _p, _l, _i, _i, _i, _f, _p],
+    "lb_token_shift": [_i, _p, _l, _p, _p, _l, _p, _p, _p, _p, _i, _i, _i, _i, _p],
+    "lb_rms_shift": [_i, _p, _l, _p, _p, _p, _l, _p, _l, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p],
+    "lb_xielu": [_i, _p, _l, _i, _i, _p, _p],
+    "lb_token_side": [_i, _p, _l, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _p],
+    "lb_latent_store": [_i, _p, _l, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p],
+    "lb_rope_heads": [_i, _i, _p, _l, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
+    "lb_head_matmul": [_i, _i, _i, _p, _l, _l, _p, _l, _l, _l, _p, _l, _l, _i, _i, _i, _i, _p],
+    "lb_head_matmul_mma_supports": [_l, _l, _l, _l, _l, _l, _l, _i, _i],
+    "lb_head_matmul_mma": [_p, _l, _l, _p, _l, _l, _l, _p, _l, _l, _i, _i, _i, _i, _p],
+    "lb_latent_attention": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
+    "lb_latent_attention_mma_supports": [_i, _i, _i, _i],
+    "lb_latent_attention_mma": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p],
+}.items():
+    _SIGNATURES[_name] = _args
+
+
+def rms_groups(x: torch.Tensor, weight: Optional[torch.Tensor], groups: int, eps: float, out: torch.Tensor,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = x[rows[r]] (or x[r]) cut into `groups` equal parts, each over its own root mean square, times weight."""
+    n = out.shape[0]
+    check(lib().lb_rms_groups(_code(out.dtype, "out"), _dev(x, "x", torch.float32), x.stride(0), _opt(rows, "rows", torch.int32),
+                              _opt(weight, "weight", torch.float32), _dev(out, "out"), out.stride(0), n, x.shape[1], groups, float(eps),
+                              stream_ptr()), "rms_groups")
+    return out
+
+
+def token_shift(h: torch.Tensor, mix: torch.Tensor, out: torch.Tensor, state: torch.Tensor, tok_seq: torch.Tensor, q_start: torch.Tensor,
+                slots: torch.Tensor, x: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None, groups: int = 1,
+                eps: float = 0.0) -> torch.Tensor:
+    """out[t] = h[t] + (h[t - 1] - h[t]) * mix with the row before a request's first row from `state` [slot, width] and its last
+    row left there.  With `x` (float32 rows) and `weight`, h is made here as rms_groups(x) in the same launch."""
+    T, S, width = h.shape[0], q_start.numel() - 1, h.shape[1]
+    decode = 1 if T == S else 0
+    layout = (_dev(tok_seq, "tok_seq", torch.int32), _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32))
+    if x is None:
+        check(lib().lb_token_shift(_code(h.dtype, "h"), _dev(h, "h"), h.stride(0), _dev(mix, "mix", torch.float32), _dev(out, "out", h.dtype),
+                                   out.stride(0), _dev(state, "state", h.dtype), *layout, T, S, decode, width, stream_ptr()), "token_shift")
+    else:
+        check(lib().lb_rms_shift(_code(h.dtype, "h"), _dev(x, "x", torch.float32), x.stride(0), _dev(weight, "weight", torch.float32),
+                                 _dev(mix, "mix", torch.float32), _dev(h, "h"), h.stride(0), _dev(out, "out", h.dtype), out.stride(0),
+                                 _dev(state, "state", h.dtype), *layout, T, S, decode, width, groups, float(eps), stream_ptr()), "rms_shift")
+    return out
+
+
+def xielu(z: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """In place over the rows of z: z > 0 -> softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+    check(lib().lb_xielu(_code(z.dtype, "z"), _dev(z, "z"), z.stride(0), z.shape[0], z.shape[1], _dev(pq, "pq", torch.float32), stream_ptr()), "xielu")
+    return z
+
+
+def token_side(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate: torch.Tensor, proj: torch.Tensor, weight: torch.Tensor,
+               eps: float) -> torch.Tensor:
+    """x[t] += rms(proj (gelu_tanh(gate x[t]) * table[tokens[t]])) * weight, in place (the kernels for steps of few tokens)."""
+    T, width, dim = x.shape[0], x.shape[1], gate.shape[0]
+    scratch = torch.empty(T * dim, dtype=torch.float32, device=x.device)
+    check(lib().lb_token_side(_code(gate.dtype, "gate"), _dev(x, "x", torch.float32), x.stride(0), _dev(tokens, "tokens", torch.int32),
+                              _dev(table, "table", gate.dtype), _dev(gate, "gate"), _dev(proj, "proj", gate.dtype), _dev(weight, "weight", torch.float32),
+                              _dev(scratch, "scratch"), T, width, dim, float(eps), stream_ptr()), "token_side")
+    return x
+
+
+def latent_store(d: torch.Tensor, gain: torch.Tensor, freq: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor,
+                 rank: int, rot: int, rot_dims: int, eps: float) -> None:
+    """Row t of d (float32 [rank | rot]) -> the RMS-normed latent and the rotated key part, into the cache rows [slot, rank + rot]."""
+    check(lib().lb_latent_store(_code(cache.dtype, "cache"), _dev(d, "d", torch.float32), d.stride(0), _dev(gain, "gain", torch.float32),
+                                _dev(freq, "freq", torch.float32), _dev(positions, "positions", torch.int32),
+                                _dev(slot_mapping, "slot_mapping", torch.int32), _dev(cache, "cache"), d.shape[0], rank, rot, rot_dims, float(eps),
+                                stream_ptr()), "latent_store")
+
+
+def rope_heads(q: torch.Tensor, freq: torch.Tensor, positions: torch.Tensor, wide: torch.Tensor, n_head: int, dim: int, rot: int, rot_dims: int,
+               rank: int) -> torch.Tensor:
+    """The rotated parts of the queries [T, H * (dim + rot)] (float32) into the wide queries [T, H * (rank + rot)]."""
+    check(lib().lb_rope_heads(_code(q.dtype, "q"), _code(wide.dtype, "wide"), _dev(q, "q"), q.stride(0), _dev(freq, "freq", torch.float32),
+                              _dev(positions, "positions", torch.int32), _dev(wide, "wide"), wide.stride(0), q.shape[0], n_head, dim, rot, rot_dims, rank,
+                              stream_ptr()), "rope_heads")
+    return wide
+
+
+def head_matmul(a: torch.Tensor, a_head: int, b: torch.Tensor, b_head: int, b_k: int, b_n: int, c: torch.Tensor, c_head: int, n: int, k: int,
+                n_head: int, tensor_cores: bool = False) -> torch.Tensor:
+    """c[t, h * c_head + j] = sum_i a[t, h * a_head + i] * b.flat[h * b_head + i * b_k + j * b_n] for j < n, i < k, every head h."""
+    m = a.shape[0]
+    if tensor_cores:
+        if not lib().lb_head_matmul_mma_supports(a.stride(0), a_head, b_head, b_k, b_n, c.stride(0), c_head, n, k):
+            raise invalid_argument("head_matmul: the tensor-core kernel does not take these strides")
+        check(lib().lb_head_matmul_mma(_dev(a, "a", torch.float32), a.stride(0), a_head, _dev(b, "b", torch.bfloat16), b_head, b_k, b_n,
+                                       _dev(c, "c", torch.bfloat16), c.stride(0), c_head, m, n, k, n_head, stream_ptr()), "head_matmul_mma")
+    else:
+        check(lib().lb_head_matmul(_code(a.dtype, "a"), _code(b.dtype, "b"), _code(c.dtype, "c"), _dev(a, "a"), a.stride(0), a_head, _dev(b, "b"),
+                                   b_head, b_k, b_n, _dev(c, "c"), c.stride(0), c_head, m, n, k, n_head, stream_ptr()), "head_matmul")
+    return c
+
+
+def latent_attention(wide: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, positions: torch.Tensor, q_start: torch.Tensor,
+                     n_past: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor, n_head: int, rank: int, rot: int, page_size: int,
+                     scale: float, window: int, tensor_cores: bool = False, n_splits: int = 1) -> torch.Tensor:
+    """out[t, h, :rank] = softmax attention of the wide queries over the latent cache rows [slot, rank + rot] of the token's request.
+    `tensor_cores`: the bfloat16 kernel (wide queries and cache bfloat16), optionally with every request's keys cut into n_splits parts."""
+    T, S = wide.shape[0], q_start.numel() - 1
+    if tensor_cores:
+        if not lib().lb_latent_attention_mma_supports(n_head, rank, rot, page_size):
+            raise invalid_argument("latent_attention: the tensor-core kernel does not take this shape")
+        max_q = int((q_start[1:] - q_start[:-1]).max().item())
+        part_o = torch.empty(max(1, n_splits * T * n_head * rank), dtype=torch.float32, device=wide.device)
+        part_ml = torch.empty(max(1, n_splits * T * n_head * 2), dtype=torch.float32, device=wide.device)
+        check(lib().lb_latent_attention_mma(_dev(wide, "wide", torch.bfloat16), wide.stride(0), _dev(cache, "cache", torch.bfloat16),
+                                            _dev(q_start, "q_start", torch.int32), _dev(n_past, "n_past", torch.int32),
+                                            _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out", torch.float32),
+                                            out.stride(0), _dev(part_o, "part_o"), _dev(part_ml, "part_ml"), T, S, max_q, n_head, rank, rot, page_size,
+                                            float(scale), window, n_splits, 1, stream_ptr()), "latent_attention_mma")
+    else:
+        check(lib().lb_latent_attention(_code(cache.dtype, "cache"), _dev(wide, "wide", torch.float32), wide.stride(0), _dev(cache, "cache"),
+                                        _dev(tok_seq, "tok_seq", torch.int32), _dev(positions, "positions", torch.int32),
+                                        _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out", torch.float32),
+                                        out.stride(0), T, n_head, rank, rot, page_size, float(scale), window, stream_ptr()), "latent_attention")
+    return out
