@@ -213,10 +213,10 @@ int lb_latent_prepare(const float* qd, int64_t ldq, const void* uk, const float*
  * in one launch; values bfloat16. */
 int lb_latent_finish(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values, int64_t ldv,
                      int n_tokens, int n_head, int rank, int vdim, int n_splits, void* stream);
-/* lb_head_matmul on the tensor cores: A float (rounded to bfloat16 on the way in), B and C bfloat16; lb_head_matmul_mma_supports says
+/* lb_head_matmul on the tensor cores: A float (rounded to bfloat16 on the way in) or bfloat16, B and C bfloat16; lb_head_matmul_mma_supports says
  * whether the strides fit its 16-byte pieces (one of b_k, b_n is 1). */
 int lb_head_matmul_mma_supports(int64_t lda, int64_t a_head, int64_t b_head, int64_t b_k, int64_t b_n, int64_t ldc, int64_t c_head, int N, int K);
-int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
+int lb_head_matmul_mma(int a_dtype, const void* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
                        int64_t c_head, int M, int N, int K, int n_head, void* stream);
 /* The same attention on the tensor cores for bfloat16 wide queries and cache rows (lb_latent_attention_mma_supports: rank one of
  * 32, 64, 96, 128, 192, 256, 384, 512; rot a multiple of 16).  Request i brings rows q_start[i] .. q_start[i + 1] - 1, the first at
@@ -224,6 +224,11 @@ int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, const void* 
  * part_o (n_splits * n_tokens * n_head * rank floats) and part_ml (n_splits * n_tokens * n_head * 2 floats), merged by a second launch
  * (or, with merge_parts 0, left for lb_latent_finish; one part is always written to out as it is). */
 int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size);
+/* The kernel for runs of tokens (64 rows a block, rank up to 256) by itself, with the attended latents out as bfloat16. */
+int lb_latent_attention_rows_supports(int n_head, int rank, int rot, int page_size);
+int lb_latent_attention_rows16(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                               const int32_t* block_table, int table_stride, void* out, int64_t ldo, int n_tokens, int n_seq, int max_q_len,
+                               int n_head, int rank, int rot, int page_size, float scale, int window, void* stream);
 int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
                             const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
                             int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,

@@ -248,10 +248,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
 // all 32 keys of a tile and all rank values.  Maxima and sums stay inside the warp (four lanes share a row), the weights pass from the
 // score accumulators straight into the next product's operand registers, and the only block-wide meeting is the change of key tiles.
 // N8: 8-column tiles of the rank values (rank = 8 * N8, N8 even).
-template <int N8>
+template <int N8, typename TO>
 __global__ void __launch_bounds__(128)
 latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
-                             const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
+                             const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride, TO* __restrict__ out,
                              int64_t ldo, int n_head, int rot, int page_size, float scale_log2, int window, int HB) {
     constexpr int M = 64, RANK = 8 * N8;
     const int D = RANK + rot, DS = D + 8, chunks = D / 8;
@@ -399,21 +399,24 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
         const int row = warp * 16 + g + 8 * half, tok = row / HB, head = hg * HB + row % HB;
         if (tok >= n_here || head >= n_head) continue;
         const float inv = 1.0f / l_run[half];
-        float* dst = out + (size_t)(first + tok) * ldo + (size_t)head * RANK + 2 * t4;
+        TO* dst = out + (size_t)(first + tok) * ldo + (size_t)head * RANK + 2 * t4;
 #pragma unroll
-        for (int nt = 0; nt < N8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+        for (int nt = 0; nt < N8; ++nt) {
+            if constexpr (sizeof(TO) == 4) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+            else *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) = __floats2bfloat162_rn(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+        }
     }
 }
 
-template <int N8>
+template <int N8, typename TO>
 int launch_rows(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table, int table_stride,
-                float* out, int64_t ldo, int n_seq, int max_q_len, int n_head, int rot, int page_size, float scale, int window, cudaStream_t s) {
+                TO* out, int64_t ldo, int n_seq, int max_q_len, int n_head, int rot, int page_size, float scale, int window, cudaStream_t s) {
     // Up to sixteen heads of a token side by side (more heads: groups of equal size), then the next tokens.
     const int groups = (n_head + 15) / 16, HB = (n_head + groups - 1) / groups, TOK = 64 / HB, DS = 8 * N8 + rot + 8;
     const size_t smem = (size_t)(64 + 2 * kKeys) * DS * sizeof(bf16);
-    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_rows_kernel<N8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_rows_kernel<N8, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, (n_head + HB - 1) / HB);
-    LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_rows_kernel<N8>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start, n_past,
+    LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_rows_kernel<N8, TO>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start, n_past,
                                        block_table, table_stride, out, ldo, n_head, rot, page_size, scale * 1.4426950408889634f, window, HB));
     return LB_OK;
 }
@@ -447,11 +450,11 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
 // C[t, h * c_head + n] = sum_k A[t, h * a_head + k] * B[h * b_head + k * b_k + n * b_n]: the products per head around the attention
 // (the keys' maps moved onto the queries; the values' maps on the attended latents) on the tensor cores.  A is float (rounded to
 // bfloat16 as it is staged), B and C bfloat16.  A block makes 64 rows x 64 columns of one head, a warp 16 of the rows; K in chunks of 32.
-// KN: B's rows run along n (b_n = 1), else along k (b_k = 1).  KC: K in chunks of that many (32; 128 for steps of few rows, whose
-// blocks then make fewer round trips to memory).
-template <bool KN, int KC>
+// KN: B's rows run along n (b_n = 1), else along k (b_k = 1).  KC: K in chunks of that many (64; 128 for steps of few rows, whose
+// blocks then make fewer round trips to memory).  A is float or bfloat16.
+template <bool KN, int KC, typename TA>
 __global__ void __launch_bounds__(128)
-head_matmul_mma_kernel(const float* __restrict__ A, int64_t lda, int64_t a_head, const bf16* __restrict__ B, int64_t b_head, int64_t b_k, int64_t b_n,
+head_matmul_mma_kernel(const TA* __restrict__ A, int64_t lda, int64_t a_head, const bf16* __restrict__ B, int64_t b_head, int64_t b_k, int64_t b_n,
                        bf16* __restrict__ C, int64_t ldc, int64_t c_head, int M, int N, int K) {
     __shared__ __align__(16) bf16 As[64][KC + 8];
     __shared__ __align__(16) bf16 Bs[KN ? KC : 64][KN ? 72 : KC + 8];
@@ -459,16 +462,22 @@ head_matmul_mma_kernel(const float* __restrict__ A, int64_t lda, int64_t a_head,
     lb_dependents_may_launch();
     const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const float* a = A + (size_t)h * a_head;
+    const TA* a = A + (size_t)h * a_head;
     const bf16* b = B + (size_t)h * b_head;
     float acc[8][4] = {};
     for (int k0 = 0; k0 < K; k0 += KC) {
         for (int idx = threadIdx.x; idx < 64 * (KC / 4); idx += 128) {      // 64 rows x groups of four values
             const int r = idx / (KC / 4), k = (idx % (KC / 4)) * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (m0 + r < M && k0 + k < K) v = *reinterpret_cast<const float4*>(a + (size_t)(m0 + r) * lda + k0 + k);
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-            *reinterpret_cast<uint2*>(&As[r][k]) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            if constexpr (sizeof(TA) == 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (m0 + r < M && k0 + k < K) v = *reinterpret_cast<const float4*>(a + (size_t)(m0 + r) * lda + k0 + k);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                *reinterpret_cast<uint2*>(&As[r][k]) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+                uint2 v = make_uint2(0u, 0u);
+                if (m0 + r < M && k0 + k < K) v = *reinterpret_cast<const uint2*>(a + (size_t)(m0 + r) * lda + k0 + k);
+                *reinterpret_cast<uint2*>(&As[r][k]) = v;
+            }
         }
         if (KN) {
             for (int idx = threadIdx.x; idx < KC * 8; idx += 128) {         // k rows x 8 pieces of eight n
@@ -552,7 +561,7 @@ extern "C" int lb_head_matmul_mma_supports(int64_t lda, int64_t a_head, int64_t 
                    c_head % 2 == 0 && N % 2 == 0 ? 1 : 0;
 }
 
-extern "C" int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
+extern "C" int lb_head_matmul_mma(int a_dtype, const void* A, int64_t lda, int64_t a_head, const void* B, int64_t b_head, int64_t b_k, int64_t b_n, void* C, int64_t ldc,
                                   int64_t c_head, int M, int N, int K, int n_head, void* stream) {
     if (!lb_head_matmul_mma_supports(lda, a_head, b_head, b_k, b_n, ldc, c_head, N, K))
         return lb_fail(LB_ERR_UNSUPPORTED, "product per head on tensor cores: strides or sizes off its 16-byte pieces");
@@ -560,14 +569,20 @@ extern "C" int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, c
     if (M == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     const dim3 grid((N + 63) / 64, (M + 63) / 64, n_head);
-#define LB_HEADS(KN, KC) LB_CHECK_CUDA(lb_launch_overlapped(head_matmul_mma_kernel<KN, KC>, grid, dim3(128), 0, s, A, lda, a_head, (const bf16*)B, b_head, b_k, \
-                                                            b_n, (bf16*)C, ldc, c_head, M, N, K))
+    LB_CHECK_ARG(a_dtype == LB_F32 || a_dtype == LB_BF16, "product per head: unknown dtype %d", a_dtype);
+#define LB_HEADS(KN, KC)                                                                                                                                    \
+    if (a_dtype == LB_F32)                                                                                                                                  \
+        LB_CHECK_CUDA(lb_launch_overlapped(head_matmul_mma_kernel<KN, KC, float>, grid, dim3(128), 0, s, (const float*)A, lda, a_head, (const bf16*)B, b_head, b_k, \
+                                           b_n, (bf16*)C, ldc, c_head, M, N, K));                                                                           \
+    else                                                                                                                                                    \
+        LB_CHECK_CUDA(lb_launch_overlapped(head_matmul_mma_kernel<KN, KC, bf16>, grid, dim3(128), 0, s, (const bf16*)A, lda, a_head, (const bf16*)B, b_head, b_k,  \
+                                           b_n, (bf16*)C, ldc, c_head, M, N, K))
     if (b_n == 1) {
-        if (M <= 64) LB_HEADS(true, 128);
-        else LB_HEADS(true, 32);
+        if (M <= 64) { LB_HEADS(true, 128); }
+        else { LB_HEADS(true, 64); }
     } else {
-        if (M <= 64) LB_HEADS(false, 128);
-        else LB_HEADS(false, 32);
+        if (M <= 64) { LB_HEADS(false, 128); }
+        else { LB_HEADS(false, 64); }
     }
 #undef LB_HEADS
     return LB_OK;
@@ -575,6 +590,26 @@ extern "C" int lb_head_matmul_mma(const float* A, int64_t lda, int64_t a_head, c
 
 extern "C" int lb_latent_attention_mma_supports(int n_head, int rank, int rot, int page_size) {
     return n_head > 0 && built_rank(rank) && rot >= 0 && rot % 16 == 0 && page_size > 0 && mma_smem_bytes(32, rank, rot) <= 200 * 1024 ? 1 : 0;
+}
+
+extern "C" int lb_latent_attention_rows_supports(int n_head, int rank, int rot, int page_size) {
+    return lb_latent_attention_mma_supports(n_head, rank, rot, page_size) && rank <= 256 && (size_t)(64 + 2 * kKeys) * (rank + rot + 8) * sizeof(bf16) <= 200 * 1024 ? 1 : 0;
+}
+
+// The 64-row kernel with the attended latents written as bfloat16 (what the values' product on the tensor cores reads).
+extern "C" int lb_latent_attention_rows16(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                          const int32_t* block_table, int table_stride, void* out, int64_t ldo, int n_tokens, int n_seq, int max_q_len,
+                                          int n_head, int rank, int rot, int page_size, float scale, int window, void* stream) {
+    if (!lb_latent_attention_rows_supports(n_head, rank, rot, page_size))
+        return lb_fail(LB_ERR_UNSUPPORTED, "latent attention, 64 rows a block: rank %d, rot %d are not built", rank, rot);
+    if (n_tokens == 0 || n_seq == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+#define LB_ROWS16(N8) \
+    if (rank == 8 * N8) return launch_rows<N8, bf16>(wide, ldw, cache, q_start, n_past, block_table, table_stride, (bf16*)out, ldo, n_seq, max_q_len, n_head, rot, \
+                                                     page_size, scale, window, s)
+    LB_ROWS16(4); LB_ROWS16(8); LB_ROWS16(12); LB_ROWS16(16); LB_ROWS16(24); LB_ROWS16(32);
+#undef LB_ROWS16
+    return lb_fail(LB_ERR_UNSUPPORTED, "latent attention, 64 rows a block: rank %d is not built", rank);
 }
 
 extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
@@ -590,7 +625,7 @@ extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void
     // Runs of tokens with a latent of up to 256 values: 64 rows a block, every warp with rows of its own.
     if (max_q_len > 1 && n_splits == 1 && rank <= 256 && (size_t)(64 + 2 * kKeys) * (rank + rot + 8) * sizeof(bf16) <= 200 * 1024) {
 #define LB_ROWS(N8) \
-    if (rank == 8 * N8) return launch_rows<N8>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, n_seq, max_q_len, n_head, rot, page_size, \
+    if (rank == 8 * N8) return launch_rows<N8, float>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, n_seq, max_q_len, n_head, rot, page_size, \
                                                scale, window, s)
         LB_ROWS(4); LB_ROWS(8); LB_ROWS(12); LB_ROWS(16); LB_ROWS(24); LB_ROWS(32);
 #undef LB_ROWS

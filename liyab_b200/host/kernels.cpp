@@ -336,9 +336,8 @@ void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t*
 
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
                  int64_t c_head, int m, int n, int k, int n_head) {
-    if (a.dtype == DType::F32 && b.dtype == DType::BF16 && c.dtype == DType::BF16 &&
-        lb_head_matmul_mma_supports(a.stride, a_head, b_head, b_k, b_n, c.stride, c_head, n, k)) {
-        check(lb_head_matmul_mma(a.f32(), a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride, c_head, m, n, k, n_head, s), "head_matmul_mma");
+    if (b.dtype == DType::BF16 && c.dtype == DType::BF16 && lb_head_matmul_mma_supports(a.stride, a_head, b_head, b_k, b_n, c.stride, c_head, n, k)) {
+        check(lb_head_matmul_mma(code(a.dtype, "a"), a.data, a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride, c_head, m, n, k, n_head, s), "head_matmul_mma");
         return;
     }
     check(lb_head_matmul(code(a.dtype, "a"), code(b.dtype, "b"), code(c.dtype, "c"), a.data, a.stride, a_head, b.data, b_head, b_k, b_n, c.data, c.stride,
@@ -359,6 +358,15 @@ void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, co
     if (attended.dtype != DType::F32 || uv.dtype != DType::BF16 || values.dtype != DType::BF16) throw invalid_argument("latent values: float32 latents, bfloat16 map and values");
     check(lb_latent_finish(attended.f32(), attended.stride, part_o, part_ml, uv.data, values.data, values.stride, n_tokens, a.n_head, a.rank, a.vdim, n_splits, s),
           "latent_finish");
+}
+
+bool latent_rows_supports(const LatentShape& a) { return lb_latent_attention_rows_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }
+
+void latent_attention_rows16(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
+                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a) {
+    if (wide.dtype != DType::BF16 || out.dtype != DType::BF16) throw invalid_argument("latent attention, 64 rows a block: bfloat16 wide queries and attended latents");
+    check(lb_latent_attention_rows16(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_tokens, n_seq, max_q_len,
+                                     a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, s), "latent_attention_rows16");
 }
 
 bool latent_mma_supports(const LatentShape& a) { return lb_latent_attention_mma_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }

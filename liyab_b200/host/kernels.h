@@ -143,6 +143,10 @@ void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, co
 // The tensor-core kernel (bfloat16 wide queries and cache): whether it takes the shape, into how many parts a decode step's keys are cut
 // (a function of the step's shape and the longest span a query can see, so a recorded step and an eager one cut alike), and the launch.
 bool latent_mma_supports(const LatentShape& a);
+// Runs of tokens, latents of up to 256 values: 64 rows a block, the attended latents out as bfloat16 for the values' product.
+bool latent_rows_supports(const LatentShape& a);
+void latent_attention_rows16(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
+                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a);
 int latent_splits(int n_seq, int n_head, int span);
 void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                           int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,

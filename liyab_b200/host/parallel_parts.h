@@ -150,9 +150,15 @@ public:
                                              static_cast<size_t>(T), s));
         }
         ctx.tap("latent.wide", wide);
-        const Rows attended = ws.get("latent.attended", T, static_cast<int64_t>(a.n_head) * a.rank, DType::F32);
+        // Steps with runs of tokens hand the attended latents on as bfloat16 where the 64-row kernel takes the shape.
+        const bool rows16 = tensor && !few && ctx.max_q_len > 1 && kernels::latent_rows_supports(shape);
+        const Rows attended = rows16 ? ws.get("latent.attended16", T, static_cast<int64_t>(a.n_head) * a.rank, DType::BF16)
+                                     : ws.get("latent.attended", T, static_cast<int64_t>(a.n_head) * a.rank, DType::F32);
         const Rows values = ws.get("latent.values", T, static_cast<int64_t>(a.n_head) * a.vdim, dt);
-        if (tensor) {
+        if (rows16) {
+            kernels::latent_attention_rows16(s, wide, cache, ctx.q_start, ctx.n_past, view->block_table, view->table_width, attended, T, ctx.n_seq,
+                                             ctx.max_q_len, shape);
+        } else if (tensor) {
             // A decode step's keys are cut over several blocks so that a few requests still fill the GPU.
             const int span = a.window > 0 ? std::min(a.window, ctx.max_positions) : ctx.max_positions;
             const int splits = ctx.decode_only ? kernels::latent_splits(ctx.n_seq, a.n_head, span) : 1;

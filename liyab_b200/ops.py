@@ -486,7 +486,7 @@ for _name, _args in {
     "lb_rope_heads": [_i, _i, _p, _l, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
     "lb_head_matmul": [_i, _i, _i, _p, _l, _l, _p, _l, _l, _l, _p, _l, _l, _i, _i, _i, _i, _p],
     "lb_head_matmul_mma_supports": [_l, _l, _l, _l, _l, _l, _l, _i, _i],
-    "lb_head_matmul_mma": [_p, _l, _l, _p, _l, _l, _l, _p, _l, _l, _i, _i, _i, _i, _p],
+    "lb_head_matmul_mma": [_i, _p, _l, _l, _p, _l, _l, _l, _p, _l, _l, _i, _i, _i, _i, _p],
     "lb_latent_attention": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_latent_attention_mma_supports": [_i, _i, _i, _i],
     "lb_latent_attention_mma": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p],
@@ -564,7 +564,7 @@ def head_matmul(a: torch.Tensor, a_head: int, b: torch.Tensor, b_head: int, b_k:
     if tensor_cores:
         if not lib().lb_head_matmul_mma_supports(a.stride(0), a_head, b_head, b_k, b_n, c.stride(0), c_head, n, k):
             raise invalid_argument("head_matmul: the tensor-core kernel does not take these strides")
-        check(lib().lb_head_matmul_mma(_dev(a, "a", torch.float32), a.stride(0), a_head, _dev(b, "b", torch.bfloat16), b_head, b_k, b_n,
+        check(lib().lb_head_matmul_mma(_code(a.dtype, "a"), _dev(a, "a"), a.stride(0), a_head, _dev(b, "b", torch.bfloat16), b_head, b_k, b_n,
                                        _dev(c, "c", torch.bfloat16), c.stride(0), c_head, m, n, k, n_head, stream_ptr()), "head_matmul_mma")
     else:
         check(lib().lb_head_matmul(_code(a.dtype, "a"), _code(b.dtype, "b"), _code(c.dtype, "c"), _dev(a, "a"), a.stride(0), a_head, _dev(b, "b"),
