@@ -107,23 +107,39 @@ __device__ __forceinline__ float softplus(float v) { return fmaxf(v, 0.0f) + log
 
 __device__ __forceinline__ float xielu_of(float v, float a, float b) { return v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v); }
 
-// VEC: rows start on 16-byte boundaries and hold a multiple of a 16-byte piece, so a thread takes a piece at a time.
+// VEC: rows start on 16-byte boundaries and hold a multiple of a 16-byte piece; a thread takes four pieces, all asked for before any is
+// used, the pieces of all rows numbered through.
 template <typename T, bool VEC>
-__global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int cols, const float* __restrict__ pq) {
+__global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int n_rows, int cols, const float* __restrict__ pq) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const float a = softplus(pq[0]), b = 0.5f + softplus(pq[1]);
-    T* row = z + (size_t)blockIdx.x * ldz;
     if (VEC) {
         constexpr int N = 16 / sizeof(T);
-        for (int i = (threadIdx.x + blockIdx.y * blockDim.x) * N; i < cols; i += blockDim.x * gridDim.y * N) {
-            uint4 raw = *reinterpret_cast<uint4*>(row + i);
-            T* v = reinterpret_cast<T*>(&raw);
+        const int per_row = cols / N;
+        const long long total = (long long)n_rows * per_row, threads = (long long)gridDim.x * blockDim.x;
+        const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        uint4 raw[4];
+        T* at[4];
 #pragma unroll
-            for (int k = 0; k < N; ++k) v[k] = lb_from_float<T>(xielu_of(lb_to_float(v[k]), a, b));
-            *reinterpret_cast<uint4*>(row + i) = raw;
+        for (int k = 0; k < 4; ++k) {
+            const long long idx = first + k * threads;
+            at[k] = nullptr;
+            if (idx < total) {
+                at[k] = z + (size_t)(idx / per_row) * ldz + (size_t)(idx % per_row) * N;
+                raw[k] = *reinterpret_cast<const uint4*>(at[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (at[k] == nullptr) continue;
+            T* v = reinterpret_cast<T*>(&raw[k]);
+#pragma unroll
+            for (int e = 0; e < N; ++e) v[e] = lb_from_float<T>(xielu_of(lb_to_float(v[e]), a, b));
+            *reinterpret_cast<uint4*>(at[k]) = raw[k];
         }
     } else {
+        T* row = z + (size_t)blockIdx.x * ldz;
         for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) row[i] = lb_from_float<T>(xielu_of(lb_to_float(row[i]), a, b));
     }
 }
@@ -192,6 +208,14 @@ __global__ void rows_to_bf16_kernel(const float* __restrict__ x, int64_t ldx, __
     lb_dependents_may_launch();
     const float* in = x + (size_t)blockIdx.x * ldx;
     __nv_bfloat16* out = y + (size_t)blockIdx.x * ldy;
+    if (cols % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+        for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(in + i);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<uint2*>(out + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < cols; i += blockDim.x) out[i] = __float2bfloat16_rn(in[i]);
 }
 
@@ -297,13 +321,14 @@ extern "C" int lb_xielu(int dtype, void* z, int64_t ldz, int n_rows, int cols, c
     auto s = static_cast<cudaStream_t>(stream);
     const int piece = dtype == LB_F32 ? 4 : 8;
     const bool vec = cols % piece == 0 && ldz % piece == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
-    const dim3 grid(n_rows, vec ? (cols / piece + 255) / 256 : (cols + 2047) / 2048);
+    const long long pieces = (long long)n_rows * (cols / piece);
+    const dim3 grid = vec ? dim3((unsigned)((pieces + 1023) / 1024)) : dim3(n_rows, (cols + 2047) / 2048);
     if (dtype == LB_F32) {
-        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, true>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
-        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, false>, grid, dim3(256), 0, s, (float*)z, ldz, cols, pq));
+        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, true>, grid, dim3(256), 0, s, (float*)z, ldz, n_rows, cols, pq));
+        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<float, false>, grid, dim3(256), 0, s, (float*)z, ldz, n_rows, cols, pq));
     } else if (dtype == LB_BF16) {
-        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
-        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, cols, pq));
+        if (vec) LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, n_rows, cols, pq));
+        else LB_CHECK_CUDA(lb_launch_overlapped(xielu_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, s, (__nv_bfloat16*)z, ldz, n_rows, cols, pq));
     } else return lb_fail(LB_ERR_INVALID_ARGUMENT, "xielu: unknown dtype %d", dtype);
     return LB_OK;
 }
