@@ -39,6 +39,8 @@ int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float
 int lb_kv_append(int dtype, const void* k, const void* v, int64_t row_stride, const int32_t* slot_mapping, void* cache,
                  int n_tokens, int n_kv_head, int head_dim, int page_size, void* stream);
 
+/* Activations of the products' epilogues (`act`): 0 none, 1 GELU (tanh form), 2 GELU (erf form), 3 xIELU (z > 0: a z^2 + z/2, else
+ * b (exp(z) - 1 - z) + z/2 with a = softplus(p), b = 1/2 + softplus(q)); with 3 the bias holds N + 2 floats, bias[N] = p, bias[N + 1] = q. */
 /* out[M,N] = act(A[M,K] . W[N,K]^T + bias) + residual on the 32-bit units; bias
  * and residual (float, row stride ldr) may be null; out may alias residual. */
 int lb_gemm_ffma(int in_dtype, int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,

@@ -33,6 +33,9 @@ enum lb_activation : int {
     LB_ACT_NONE = 0,
     LB_ACT_GELU_TANH = 1,
     LB_ACT_GELU_ERF = 2,
+    // xIELU: z > 0 -> a z^2 + z/2, else b (exp(z) - 1 - z) + z/2 with a = softplus(p), b = 1/2 + softplus(q).  The two learned numbers
+    // travel behind the bias: a product with this activation is given a bias of N + 2 floats, bias[N] = p and bias[N + 1] = q.
+    LB_ACT_XIELU = 3,
 };
 
 int lb_fail(int code, const char* fmt, ...);
@@ -149,10 +152,31 @@ __device__ __forceinline__ float lb_gelu_erf(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
+__device__ __forceinline__ float lb_softplus(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float lb_xielu(float v, float a, float b) { return v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v); }
+
+// The two factors of an activation with learned numbers (zeros for the others), read once by a thread before its epilogue.
+struct lb_act_pair {
+    float a, b;
+};
+__device__ __forceinline__ lb_act_pair lb_act_load(const float* bias, int N, int act) {
+    lb_act_pair p{0.0f, 0.0f};
+    if (act == LB_ACT_XIELU && bias != nullptr) {
+        p.a = lb_softplus(__ldg(bias + N));
+        p.b = 0.5f + lb_softplus(__ldg(bias + N + 1));
+    }
+    return p;
+}
+
 __device__ __forceinline__ float lb_activate(float x, int act) {
     if (act == LB_ACT_GELU_TANH) return lb_gelu_tanh(x);
     if (act == LB_ACT_GELU_ERF) return lb_gelu_erf(x);
     return x;
+}
+
+__device__ __forceinline__ float lb_activate(float x, int act, const lb_act_pair& p) {
+    if (act == LB_ACT_XIELU) return lb_xielu(x, p.a, p.b);
+    return lb_activate(x, act);
 }
 
 template <typename... Params, typename... Args>

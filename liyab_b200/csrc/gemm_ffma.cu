@@ -122,6 +122,7 @@ gemm_ffma_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W
         }
         __syncthreads();
     }
+    const lb_act_pair act_pair = lb_act_load(bias, N, act);
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int gm = m0 + ty * TM + i;
@@ -132,7 +133,7 @@ gemm_ffma_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W
             if (gn >= N) continue;
             float v = tot[i][j];
             if (bias != nullptr) v += bias[gn];
-            v = lb_activate(v, act);
+            v = lb_activate(v, act, act_pair);
             if (residual != nullptr) v += residual[(size_t)gm * ldr + gn];
             out[(size_t)gm * ldo + gn] = lb_from_float<TO>(v);
         }
@@ -262,6 +263,7 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
 #pragma unroll
     for (int r = 0; r < TOKENS; ++r) red[(group * TOKENS + r) * kSkinnyFeatures + fi] = grp[r];
     __syncthreads();
+    const lb_act_pair act_pair = lb_act_load(bias, N, act);
     for (int idx = threadIdx.x; idx < TOKENS * kSkinnyFeatures; idx += blockDim.x) {
         const int r = idx / kSkinnyFeatures, ff = idx % kSkinnyFeatures;
         const int gn = blockIdx.x * kSkinnyFeatures + ff;
@@ -270,7 +272,7 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
             float v = red[(0 * TOKENS + r) * kSkinnyFeatures + ff];
             for (int g2 = 1; g2 < n_groups; ++g2) v += red[(g2 * TOKENS + r) * kSkinnyFeatures + ff];
             if (bias != nullptr) v += bias[gn];
-            v = lb_activate(v, act);
+            v = lb_activate(v, act, act_pair);
             if (residual != nullptr) v += residual[(size_t)r * ldr + gn];
             out[(size_t)r * ldo + gn] = lb_from_float<TO>(v);
         }

@@ -215,6 +215,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
         // A thread finishes at most kEarly elements of a pass (element idx = threadIdx.x + 256 e); their bias and residual
         // are asked for now and arrive under the products instead of after them.
         constexpr int kEarly = (NG * kRows * 8 + kThreads - 1) / kThreads;
+        const lb_act_pair act_pair = lb_act_load(bias, N, act);
         float2 early[kEarly];
 #pragma unroll
         for (int e = 0; e < kEarly; ++e) {
@@ -277,7 +278,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
                 float v = 0.0f;
 #pragma unroll
                 for (int wp = 0; wp < kWarps; ++wp) v += red_s[((size_t)(wp * NG + gi) * MT + m) * 128 + rr * 8 + cfeat];
-                float y = lb_activate(v + early[e].x, act);
+                float y = lb_activate(v + early[e].x, act, act_pair);
                 if (residual != nullptr) y += early[e].y;
                 out[(size_t)r * ldo + f] = lb_from_float<TO>(y);
                 if (kv.cache != nullptr && f >= kv.q_dim) {

@@ -184,6 +184,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const lb_act_pair act_pair = lb_act_load(bias, N, act);      // weights: read ahead of the wait
         lb_wait_for_predecessor();           // before the residual is read and anything is written
         lb_dependents_may_launch();
         if (!mbar_wait(&s.acc_ready, 0, abort_flag)) {
@@ -215,7 +216,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                     for (int j = 0; j < 16; ++j) {
                         float y = __uint_as_float(v[j]);
                         if (bias != nullptr) y += __ldg(bias + f0 + j);
-                        y = lb_activate(y, act);
+                        y = lb_activate(y, act, act_pair);
                         if (residual != nullptr) y += r[j];
                         x[j] = y;
                     }
@@ -227,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                         if (f < N) {
                             float y = __uint_as_float(v[j]);
                             if (bias != nullptr) y += bias[f];
-                            y = lb_activate(y, act);
+                            y = lb_activate(y, act, act_pair);
                             if (residual != nullptr) y += residual[(size_t)t * ldr + f];
                             out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
                         }
@@ -256,7 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = m0 + c + j;
-                        if (t < M) out[(size_t)t * ldo + f] = lb_from_float<TO>(lb_activate(__uint_as_float(v[j]) + b, act) + r[j]);
+                        if (t < M) out[(size_t)t * ldo + f] = lb_from_float<TO>(lb_activate(__uint_as_float(v[j]) + b, act, act_pair) + r[j]);
                     }
                 }
             }
@@ -320,7 +321,7 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial, const fl
     float acc = 0.0f;
 #pragma unroll
     for (int sp = 0; sp < 16; ++sp) acc += v[sp];
-    float y = lb_activate(acc + b, act);
+    float y = lb_activate(acc + b, act, lb_act_load(bias, N, act));
     if (residual != nullptr) y += r;
     out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
     if (kv.cache != nullptr && f >= kv.q_dim) {

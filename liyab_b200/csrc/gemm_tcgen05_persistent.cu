@@ -186,7 +186,7 @@ __device__ __forceinline__ void sts4(uint32_t addr, uint4 v) {
 // the fast exponential and division (relative error about 1e-6, far below bfloat16's rounding), a few
 // instructions instead of dozens; float32 results take the library functions.
 template <int ACT, bool FAST>
-__device__ __forceinline__ float activate(float x) {
+__device__ __forceinline__ float activate(float x, const lb_act_pair& p) {
     if constexpr (ACT == LB_ACT_GELU_TANH) {
         if constexpr (FAST) {
             const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
@@ -197,6 +197,9 @@ __device__ __forceinline__ float activate(float x) {
         }
     } else if constexpr (ACT == LB_ACT_GELU_ERF) {
         return lb_gelu_erf(x);
+    } else if constexpr (ACT == LB_ACT_XIELU) {
+        if constexpr (FAST) return x > 0.0f ? fmaf(p.a * x, x, 0.5f * x) : fmaf(p.b, __expf(x) - 1.0f - x, 0.5f * x);
+        else return lb_xielu(x, p.a, p.b);
     } else {
         return x;
     }
@@ -423,6 +426,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const bool elected = (et & 127) == 0;                          // one per group: issues and tracks its stores
         const uint32_t swz = (uint32_t)(row & 7);
         const uint32_t row_u32 = staging_u32 + (uint32_t)row * 128u;
+        const lb_act_pair act_pair = lb_act_load(bias, N, ACT);      // the learned numbers of an xIELU ride behind the bias; zeros otherwise
         lb_wait_for_predecessor();           // before anything this block stores, and before a cache page is written
         lb_dependents_may_launch();
         int it = 0;
@@ -534,10 +538,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         const uint32_t at = strip + (((uint32_t)ch ^ swz) << 4);
                         const float4 bb = lds4(b + 16 * ch);
                         float4 y;
-                        y.x = activate<ACT, false>(__uint_as_float(v[4 * ch]) + bb.x);
-                        y.y = activate<ACT, false>(__uint_as_float(v[4 * ch + 1]) + bb.y);
-                        y.z = activate<ACT, false>(__uint_as_float(v[4 * ch + 2]) + bb.z);
-                        y.w = activate<ACT, false>(__uint_as_float(v[4 * ch + 3]) + bb.w);
+                        y.x = activate<ACT, false>(__uint_as_float(v[4 * ch]) + bb.x, act_pair);
+                        y.y = activate<ACT, false>(__uint_as_float(v[4 * ch + 1]) + bb.y, act_pair);
+                        y.z = activate<ACT, false>(__uint_as_float(v[4 * ch + 2]) + bb.z, act_pair);
+                        y.w = activate<ACT, false>(__uint_as_float(v[4 * ch + 3]) + bb.w, act_pair);
                         if constexpr (HAS_RES) {
                             const float4 r = lds4(at);
                             y.x += r.x; y.y += r.y; y.z += r.z; y.w += r.w;
@@ -555,10 +559,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             const int ch = half * 4 + q;
                             const float4 b0 = lds4(b + 128 * half + 32 * q), b1 = lds4(b + 128 * half + 32 * q + 16);
                             uint4 y;
-                            y.x = pack2(activate<ACT, true>(__uint_as_float(v[8 * q]) + b0.x), activate<ACT, true>(__uint_as_float(v[8 * q + 1]) + b0.y));
-                            y.y = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 2]) + b0.z), activate<ACT, true>(__uint_as_float(v[8 * q + 3]) + b0.w));
-                            y.z = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 4]) + b1.x), activate<ACT, true>(__uint_as_float(v[8 * q + 5]) + b1.y));
-                            y.w = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 6]) + b1.z), activate<ACT, true>(__uint_as_float(v[8 * q + 7]) + b1.w));
+                            y.x = pack2(activate<ACT, true>(__uint_as_float(v[8 * q]) + b0.x, act_pair), activate<ACT, true>(__uint_as_float(v[8 * q + 1]) + b0.y, act_pair));
+                            y.y = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 2]) + b0.z, act_pair), activate<ACT, true>(__uint_as_float(v[8 * q + 3]) + b0.w, act_pair));
+                            y.z = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 4]) + b1.x, act_pair), activate<ACT, true>(__uint_as_float(v[8 * q + 5]) + b1.y, act_pair));
+                            y.w = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 6]) + b1.z, act_pair), activate<ACT, true>(__uint_as_float(v[8 * q + 7]) + b1.w, act_pair));
                             if (KV && to_cache) {
                                 if (cache_row != nullptr) cache_row[ch] = y;
                             } else {
@@ -785,6 +789,7 @@ static int launch_persistent(int out_dtype, const void* A, int64_t lda, const vo
         case LB_ACT_NONE: LB_GO(TO, LB_ACT_NONE, RES); break;               \
         case LB_ACT_GELU_TANH: LB_GO(TO, LB_ACT_GELU_TANH, RES); break;     \
         case LB_ACT_GELU_ERF: LB_GO(TO, LB_ACT_GELU_ERF, RES); break;       \
+        case LB_ACT_XIELU: LB_GO(TO, LB_ACT_XIELU, RES); break;             \
         default: return lb_fail(LB_ERR_INVALID_ARGUMENT, "gemm_persistent: unknown activation %d", act); \
     }
     if (pair) {

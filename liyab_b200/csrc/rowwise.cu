@@ -103,9 +103,7 @@ __global__ void shift_keep_kernel(const T* __restrict__ h, int64_t ldh, T* __res
 
 // ---------------------------------------------------------------- xIELU
 // z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2, with a = softplus(p) and b = 1/2 + softplus(q).
-__device__ __forceinline__ float softplus(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
-
-__device__ __forceinline__ float xielu_of(float v, float a, float b) { return v > 0.0f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v); }
+// (lb_softplus and lb_xielu of common.cuh: the same statements the products' epilogues use.)
 
 // VEC: rows start on 16-byte boundaries and hold a multiple of a 16-byte piece; a thread takes four pieces, all asked for before any is
 // used, the pieces of all rows numbered through.
@@ -113,7 +111,7 @@ template <typename T, bool VEC>
 __global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int n_rows, int cols, const float* __restrict__ pq) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
-    const float a = softplus(pq[0]), b = 0.5f + softplus(pq[1]);
+    const float a = lb_softplus(pq[0]), b = 0.5f + lb_softplus(pq[1]);
     if (VEC) {
         constexpr int N = 16 / sizeof(T);
         const int per_row = cols / N;
@@ -135,12 +133,12 @@ __global__ void xielu_kernel(T* __restrict__ z, int64_t ldz, int n_rows, int col
             if (at[k] == nullptr) continue;
             T* v = reinterpret_cast<T*>(&raw[k]);
 #pragma unroll
-            for (int e = 0; e < N; ++e) v[e] = lb_from_float<T>(xielu_of(lb_to_float(v[e]), a, b));
+            for (int e = 0; e < N; ++e) v[e] = lb_from_float<T>(lb_xielu(lb_to_float(v[e]), a, b));
             *reinterpret_cast<uint4*>(at[k]) = raw[k];
         }
     } else {
         T* row = z + (size_t)blockIdx.x * ldz;
-        for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) row[i] = lb_from_float<T>(xielu_of(lb_to_float(row[i]), a, b));
+        for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < cols; i += blockDim.x * gridDim.y) row[i] = lb_from_float<T>(lb_xielu(lb_to_float(row[i]), a, b));
     }
 }
 

@@ -239,8 +239,8 @@ public:
 };
 
 // ---- the dense, ungated feed-forward: down(act(up(x))) ----------------------------------------------
-// Activations: gelu_tanh, gelu_erf, none (in the first product's epilogue) and xielu (z > 0: softplus(p) z^2 + z/2; else
-// (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with the learned pair `act` = (p, q)).
+// Activations, all in the first product's epilogue: gelu_tanh, gelu_erf, none and xielu (z > 0: softplus(p) z^2 + z/2; else
+// (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with the learned pair `act` = (p, q), which the product finds behind its bias).
 // Reference: dense_ffn, ungated branch (src/core/transformer.cpp:4903-4913) with the activations of :125-142.
 // Bias and activation ride in the first product's epilogue, bias and the residual sum in the second's.
 
@@ -249,9 +249,9 @@ public:
     DenseFeedForward(const PartSpec& s, const Params& p) {
         inner = need_int(s, "inner");
         const std::string act = s.options.get_string("activation", "gelu_tanh");
-        // The xIELU has two learned numbers of its own and runs as a kernel between the two products.
+        // The xIELU has two learned numbers of its own; they ride behind the first product's bias into its epilogue.
         if (act == "xielu") xielu = f32_or_null(&p.at("act"));
-        activation = act == "xielu" ? kernels::kNone : kernels::activation_from_name(act);
+        activation = kernels::activation_from_name(act);
         up = Linear(p, "up.", "feed_forward.up");
         down = Linear(p, "down.", "feed_forward.down");
     }
@@ -268,8 +268,11 @@ public:
     void forward(StepContext& ctx, const Rows& h, const Rows& x) override {
         const int T = ctx.n_tokens;
         const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
-        up.forward(ctx, h, mid, T, activation);
-        if (xielu != nullptr) kernels::xielu(ctx.stream(), mid, T, xielu);
+        if (xielu != nullptr) {
+            kernels::linear(ctx.runtime, ctx.workspace, h, up.weight, bias_and_pair(ctx.stream()), mid, T, activation, nullptr);
+        } else {
+            up.forward(ctx, h, mid, T, activation);
+        }
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
     }
     // As the attention's: the up projection of a few tokens normalises the rows inside its kernel.
@@ -285,6 +288,20 @@ public:
     int activation = 0;
     const float* xielu = nullptr;      // the activation's two learned numbers (p, q), where it is the xIELU
     Linear up, down;
+
+private:
+    // [bias (or zeros) | p | q] on the device, put together at the first step (which is never a recorded one).
+    const float* bias_and_pair(cudaStream_t s) {
+        if (joined_.data() == nullptr) {
+            joined_ = DeviceBuffer(static_cast<size_t>(inner + 2) * sizeof(float), true);
+            char* base = static_cast<char*>(joined_.data());
+            if (up.bias != nullptr) LIYAB_CUDA(cudaMemcpyAsync(base, up.bias, static_cast<size_t>(inner) * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            LIYAB_CUDA(cudaMemcpyAsync(base + static_cast<size_t>(inner) * sizeof(float), xielu, 2 * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            LIYAB_CUDA(cudaStreamSynchronize(s));
+        }
+        return static_cast<const float*>(joined_.data());
+    }
+    DeviceBuffer joined_;
 };
 
 // ---- how a layer's parts are arranged around the residual stream ---------------------------------------

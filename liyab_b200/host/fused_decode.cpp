@@ -57,6 +57,7 @@ std::unique_ptr<FusedDecodeStack> FusedDecodeStack::try_build(const DecoderModel
         s->max_heads_ = std::max(s->max_heads_, a.n_head);
         s->max_kv_heads_ = std::max(s->max_kv_heads_, a.n_kv_head);
         s->max_k_ = std::max({s->max_k_, qd, static_cast<int>(ff->inner)});
+        if (ff->xielu != nullptr) return nullptr;            // the one-kernel step knows the activations without learned numbers only
         LayerRecord r{};
         const void* ptrs[13] = {n1->weight_, n1->bias_, n2->weight_, n2->bias_, at->qkv.weight.data, at->qkv.bias, at->out.weight.data,
                                 at->out.bias, ff->up.weight.data, ff->up.bias, ff->down.weight.data, ff->down.bias,

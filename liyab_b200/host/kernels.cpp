@@ -21,7 +21,8 @@ int activation_from_name(const std::string& name) {
     if (name == "none") return kNone;
     if (name == "gelu_tanh") return kGeluTanh;
     if (name == "gelu_erf") return kGeluErf;
-    throw unsupported("activation '{}' is not supported; supported: gelu_tanh, gelu_erf, none", name);
+    if (name == "xielu") return kXielu;
+    throw unsupported("activation '{}' is not supported; supported: gelu_tanh, gelu_erf, xielu, none", name);
 }
 
 namespace {

@@ -22,7 +22,8 @@ extern std::atomic<uint64_t> launches;
 
 void check(int status, const char* what);
 
-enum Activation : int { kNone = 0, kGeluTanh = 1, kGeluErf = 2 };
+// kXielu: the activation's two learned numbers ride behind the bias (a bias of N + 2 floats: bias[N] = p, bias[N + 1] = q).
+enum Activation : int { kNone = 0, kGeluTanh = 1, kGeluErf = 2, kXielu = 3 };
 int activation_from_name(const std::string& name);      // UNSUPPORTED when unknown
 
 // Keys and values of a fused projection that go straight to a layer's cache pages.

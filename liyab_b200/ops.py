@@ -17,7 +17,7 @@ from .csrc.build import load_library
 from .status import ErrorCode, LiyabError, invalid_argument
 
 F32, BF16 = 0, 1
-ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3}      # xielu: the bias holds N + 2 values, the last two the learned pair
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 _c = ctypes

@@ -232,3 +232,42 @@ def test_latent_store_and_rotation():
     want = plain.rotate_half(q[..., dim:], positions, base, rot_dims)
     got = wide.cpu().numpy().reshape(T, H, rank + rot)
     assert np.abs(got[..., rank:] - want).max() < 2e-4 and np.abs(got[..., :rank]).max() == 0
+
+
+@pytest.mark.parametrize("m, n, k", [(5, 136, 96), (40, 200, 128), (300, 256, 192), (9, 264, 2048)])
+def test_xielu_in_the_products_epilogues(m, n, k):
+    """The activation inside every product kernel that can take the shape (its two learned numbers behind the bias) against the
+    product in float64 followed by the plain activation."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(m)
+    a, w = rng.normal(0, 1, (m, k)), rng.normal(0, k ** -0.5, (n, k))
+    bias, pq = rng.normal(0, 0.3, n), np.array([0.4, -0.8])
+    joined = dev(np.concatenate([bias, pq]))
+    a16, w16 = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    want32 = plain.xielu(a @ w.T + bias, *pq)
+    want16 = plain.xielu(a16.double().cpu().numpy() @ w16.double().cpu().numpy().T + bias, *pq)
+    scale = np.abs(want32).max()
+    out = ops.gemm_ffma(dev(a), dev(w), joined, torch.empty(m, n, device="cuda"), m, "xielu")
+    assert np.abs(out.cpu().numpy() - want32).max() < 2e-5 * scale
+    ran = 0
+    for out_dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 1e-2)):
+        if ops.gemm_rows_supports(a16, w16, m):
+            out = ops.gemm_rows(a16, w16, joined, torch.empty(m, n, dtype=out_dtype, device="cuda"), m, "xielu")
+            assert np.abs(out.float().cpu().numpy() - want16).max() < tol * scale
+            ran += 1
+        if ops.tcgen05_accepts(a16, w16):
+            out = torch.empty(m, n, dtype=out_dtype, device="cuda")
+            if m > 64 and ops.gemm_persistent_tile(a16, w16, out, m) > 0:
+                ops.gemm_persistent(a16, w16, joined, out, m, "xielu")
+            else:
+                ops.linear(a16, w16, joined, out, m, "xielu")
+            assert np.abs(out.float().cpu().numpy() - want16).max() < tol * scale
+            ran += 1
+            splits = ops.gemm_splits(m, n, k)
+            if m <= 64 and splits > 1:       # K split over blocks: the activation sits in the second launch, which adds the parts
+                partial = torch.empty(splits * m * n, device="cuda")
+                counters = torch.zeros(-(-n // 128), dtype=torch.int32, device="cuda")
+                out = ops.gemm_tcgen05(a16, w16, joined, torch.empty(m, n, dtype=out_dtype, device="cuda"), m, "xielu", None, 0, partial, counters, splits)
+                assert np.abs(out.float().cpu().numpy() - want16).max() < tol * scale
+                ran += 1
+    assert ran >= 2
