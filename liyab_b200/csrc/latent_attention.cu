@@ -146,6 +146,19 @@ latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const floa
     lb_dependents_may_launch();
     const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (n_splits > 1) {
+        // The parts' sums for this thread's first two latent values are asked for before the factors are made (up to 16 parts).
+        constexpr int kParts = 16;
+        float ahead[2][kParts];
+        const bool fits = n_splits <= kParts;
+        if (fits) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int d = threadIdx.x + k * blockDim.x;
+#pragma unroll
+                for (int s = 0; s < kParts; ++s)
+                    ahead[k][s] = (d < rank && s < n_splits) ? part_o[(((size_t)s * n_tokens + t) * n_head + h) * rank + d] : 0.0f;
+            }
+        }
         if (warp == 0) {                       // factor_s = 2^(m_s - m) / sum_s 2^(m_s - m) l_s, parts in their order
             float ms = -CUDART_INF_F, ls = 0.0f;
             if (lane < n_splits) {
@@ -160,7 +173,22 @@ latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const floa
             if (lane < n_splits) factor[lane] = e / l;
         }
         __syncthreads();
-        for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        int d_from = threadIdx.x;
+        if (fits) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int d = threadIdx.x + k * blockDim.x;
+                if (d < rank) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < kParts; ++s)
+                        if (s < n_splits) acc = fmaf(factor[s], ahead[k][s], acc);
+                    osm[d] = acc;
+                }
+            }
+            d_from = threadIdx.x + 2 * blockDim.x;
+        }
+        for (int d = d_from; d < rank; d += blockDim.x) {
             float acc = 0.0f;
 #pragma unroll 4
             for (int s = 0; s < n_splits; ++s) acc = fmaf(factor[s], part_o[(((size_t)s * n_tokens + t) * n_head + h) * rank + d], acc);

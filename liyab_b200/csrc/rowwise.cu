@@ -47,6 +47,24 @@ __global__ void rms_shift_kernel(const float* __restrict__ x, int64_t ldx, const
     const int part = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const float* cur = x + (size_t)t * ldx;
     const float* before = t > first ? x + (size_t)(t - 1) * ldx : nullptr;
+    T* keep = state + (size_t)slots[s] * width;
+    // Up to eight values a thread: its pieces of both rows, the gains and the state are asked for now, together with the sums' own
+    // loads, instead of after the sums (one round trip to memory fewer; wider rows take the loads in the loop below).
+    constexpr int kAhead = 8;
+    const bool ahead = width <= kAhead * (int)blockDim.x;
+    float a_cur[kAhead], a_prev[kAhead], a_w[kAhead], a_mu[kAhead];
+    if (ahead) {
+#pragma unroll
+        for (int e = 0; e < kAhead; ++e) {
+            const int i = threadIdx.x + e * blockDim.x;
+            if (i < width) {
+                a_cur[e] = cur[i];
+                a_prev[e] = before != nullptr ? before[i] : lb_to_float(keep[i]);
+                a_w[e] = w[i];
+                a_mu[e] = mu[i];
+            }
+        }
+    }
     // A warp per (row, group) sum: lanes stride over the part, then a shuffle tree; order fixed by the part's length.
     for (int job = warp; job < 2 * groups; job += n_warps) {
         const float* row = job < groups ? cur : before;
@@ -58,7 +76,21 @@ __global__ void rms_shift_kernel(const float* __restrict__ x, int64_t ldx, const
         if (lane == 0) inv_of[job] = 1.0f / sqrtf(ss / (float)part + eps);
     }
     __syncthreads();
-    T* keep = state + (size_t)slots[s] * width;
+    if (ahead) {
+#pragma unroll
+        for (int e = 0; e < kAhead; ++e) {
+            const int i = threadIdx.x + e * blockDim.x;
+            if (i >= width) break;
+            const int g = i / part;
+            const T hc = lb_from_float<T>(a_cur[e] * inv_of[g] * a_w[e]);
+            const T hp = lb_from_float<T>(before != nullptr ? a_prev[e] * inv_of[groups + g] * a_w[e] : a_prev[e]);
+            const float c = lb_to_float(hc), p = lb_to_float(hp);
+            h[(size_t)t * ldh + i] = hc;
+            m[(size_t)t * ldm + i] = lb_from_float<T>(c + (p - c) * a_mu[e]);
+            if (first == last) keep[i] = hc;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const int g = i / part;
         const T hc = lb_from_float<T>(cur[i] * inv_of[g] * w[i]);
@@ -195,8 +227,30 @@ side_proj_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ g
         ys[c] = acc;
         ss = fmaf(acc, acc, ss);
     }
-    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    // The row to add to and its gains: asked for before the block's sum (up to eight values a thread), not after it.
     float* xr = x + (size_t)t * ldx;
+    constexpr int kAhead = 8;
+    const bool ahead = width <= kAhead * (int)blockDim.x;
+    float a_x[kAhead], a_w[kAhead];
+    if (ahead) {
+#pragma unroll
+        for (int e = 0; e < kAhead; ++e) {
+            const int c = threadIdx.x + e * blockDim.x;
+            if (c < width) {
+                a_x[e] = xr[c];
+                a_w[e] = w[c];
+            }
+        }
+    }
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    if (ahead) {
+#pragma unroll
+        for (int e = 0; e < kAhead; ++e) {
+            const int c = threadIdx.x + e * blockDim.x;
+            if (c < width) xr[c] = a_x[e] + ys[c] * inv * a_w[e];
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) xr[c] += ys[c] * inv * w[c];
 }
 
