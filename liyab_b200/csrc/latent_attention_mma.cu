@@ -82,17 +82,6 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
     const int per = (tile_hi - tile_lo + n_splits) / n_splits;
     const int my_lo = tile_lo + split * per, my_hi = min(tile_hi, my_lo + per - 1);
 
-    // Queries: row r is token first + r / HB, head hg * HB + r % HB.
-    for (int r = warp; r < M; r += 4) {
-        const int tok = r / HB, head = hg * HB + r % HB;
-        const bool valid = tok < n_here && head < n_head;
-        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
-        for (int c = lane; c < chunks; c += 32) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
-        }
-    }
     auto load_tile = [&](int tile, int buf) {
         bf16* dst0 = ks + (size_t)buf * kKeys * DS;
         for (int key = warp; key < kKeys; key += 4) {
@@ -107,6 +96,18 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
         }
         cp_async_commit();
     };
+    if (my_lo <= my_hi) load_tile(my_lo, 0);                     // on its way while the queries are staged
+    // Queries: row r is token first + r / HB, head hg * HB + r % HB.
+    for (int r = warp; r < M; r += 4) {
+        const int tok = r / HB, head = hg * HB + r % HB;
+        const bool valid = tok < n_here && head < n_head;
+        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
+        }
+    }
 
     float o[MT][RT][4];
     float m_run[MT][2], l_run[MT][2];
@@ -120,7 +121,6 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
             for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.0f;
     }
 
-    if (my_lo <= my_hi) load_tile(my_lo, 0);
     for (int tile = my_lo; tile <= my_hi; ++tile) {
         const int buf = (tile - my_lo) & 1;
         cp_async_wait_all();
@@ -272,16 +272,6 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
     const int32_t* table = block_table + (size_t)s * table_stride;
     const int tile_lo = lo_min / kKeys, tile_hi = p_last / kKeys;
 
-    for (int r = warp; r < M; r += 4) {
-        const int tok = r / HB, head = hg * HB + r % HB;
-        const bool valid = tok < n_here && head < n_head;
-        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
-        for (int c = lane; c < chunks; c += 32) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
-        }
-    }
     auto load_tile = [&](int tile, int buf) {
         bf16* dst0 = ks + (size_t)buf * kKeys * DS;
         for (int key = warp; key < kKeys; key += 4) {
@@ -296,6 +286,17 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
         }
         cp_async_commit();
     };
+    load_tile(tile_lo, 0);                                        // on its way while the queries are staged
+    for (int r = warp; r < M; r += 4) {
+        const int tok = r / HB, head = hg * HB + r % HB;
+        const bool valid = tok < n_here && head < n_head;
+        const bf16* src = wide + (size_t)(first + min(tok, n_here - 1)) * ldw + (size_t)min(head, n_head - 1) * D;
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(qs + (size_t)r * DS + c * 8) = v;
+        }
+    }
 
     // This thread's two rows (g and g + 8 of the warp's sixteen): their tokens' positions and first visible keys.
     int p_row[2], lo_row[2];
@@ -314,7 +315,6 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
         for (int i = 0; i < 4; ++i) o[nt][i] = 0.0f;
     float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.0f, 0.0f};
 
-    load_tile(tile_lo, 0);
     for (int tile = tile_lo; tile <= tile_hi; ++tile) {
         const int buf = (tile - tile_lo) & 1;
         cp_async_wait_all();

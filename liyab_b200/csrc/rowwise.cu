@@ -189,10 +189,11 @@ side_gate_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __rest
     if (d >= dim) return;
     const T* row = G + (size_t)d * width;
     const float* xr = x + (size_t)t * ldx;
+    const float e = lb_to_float(table[(size_t)tokens[t] * dim + d]);        // asked for under the sum, not after it
     float acc = 0.0f;
     for (int c = lane; c < width; c += 32) acc = fmaf(lb_to_float(row[c]), xr[c], acc);
     acc = lb_warp_sum(acc);
-    if (lane == 0) g[(size_t)t * dim + d] = lb_gelu_tanh(acc) * lb_to_float(table[(size_t)tokens[t] * dim + d]);
+    if (lane == 0) g[(size_t)t * dim + d] = lb_gelu_tanh(acc) * e;
 }
 
 template <typename T>
