@@ -198,7 +198,11 @@ __device__ __forceinline__ float activate(float x, const lb_act_pair& p) {
     } else if constexpr (ACT == LB_ACT_GELU_ERF) {
         return lb_gelu_erf(x);
     } else if constexpr (ACT == LB_ACT_XIELU) {
-        if constexpr (FAST) return x > 0.0f ? fmaf(p.a * x, x, 0.5f * x) : fmaf(p.b, __expf(x) - 1.0f - x, 0.5f * x);
+        if constexpr (FAST) {
+            // Without a branch: the positive part feeds the square, the negative part the exponential (which then never overflows).
+            const float pos = fmaxf(x, 0.0f), neg = fminf(x, 0.0f);
+            return fmaf(p.a * pos, pos, fmaf(p.b, __expf(neg) - 1.0f - neg, 0.5f * x));
+        }
         else return lb_xielu(x, p.a, p.b);
     } else {
         return x;
