@@ -11,7 +11,7 @@
 
 #include <stdint.h>
 
-#define LB_ABI_VERSION 3
+#define LB_ABI_VERSION 4
 
 #ifdef __cplusplus
 extern "C" {
