@@ -11,7 +11,7 @@
 
 #include <stdint.h>
 
-#define LB_ABI_VERSION 4
+#define LB_ABI_VERSION 5
 
 #ifdef __cplusplus
 extern "C" {
@@ -111,7 +111,8 @@ int lb_gemm_tcgen05_status(int* status);
 /* Causal attention of every token of the step over its request's pages.
  * q: [n_tokens, n_head*head_dim] with row stride q_stride; tok_seq[t] is the row
  * of block_table (stride table_stride) of the token's request; positions[t] its
- * absolute position; window 0 = all earlier keys. */
+ * absolute position.  `window` says which earlier keys a query sees, here and in the four attention kernels below:
+ * 0 all of them; w > 0 the w latest; -c those of the query's own chunk of c positions (chunks counted from position 0). */
 int lb_paged_attention_generic(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq,
                                const int32_t* positions, const int32_t* block_table, int table_stride, void* out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
@@ -280,6 +281,49 @@ int lb_decode_stack_status_set(int value);
  * The waits run to their limit (about two seconds), set the status word and the kernel returns. */
 int lb_gemm_tcgen05_withhold_next(int on);
 int lb_decode_stack_withhold_next(int on);
+
+/* lb_rms_groups with `gain_offset` added to every gain (1 for gains stored around zero). */
+int lb_rms_groups_offset(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, float gain_offset, void* y, int64_t ldy,
+                         int n_rows, int width, int groups, float eps, void* stream);
+/* x[r,:] += v for every row. */
+int lb_add_row(float* x, int64_t ldx, const float* v, int n_rows, int width, void* stream);
+/* x[r,:] += scale * sum_i y_i[r,:] / sqrt(mean(y_i[r,:]^2) + eps) * weight_i over 1 to 4 branches; `y`, `ldy`, `weight` are host
+ * arrays of device pointers and strides (a weight, or the whole array, may be null). */
+int lb_rms_sum_add(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight, int n_rows, int width,
+                   float scale, float eps, void* stream);
+/* From the float rows proj [T, ld] holding q (n_head x dim at column q_off), k (n_kv_head x dim at k_off) and v (n_kv_head x vdim at
+ * v_off): with `norm`, every query and key head over its root mean square times q_weight / k_weight (float [dim], may be null).
+ * Queries go to q_out [T, n_head x padded], keys and values into the cache [page][K|V][kv_head][slot][padded] at slot_mapping[t]
+ * (negative: skipped; cache null: queries only); values beyond dim or vdim are zeros. */
+int lb_qk_norm_store(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight, const float* k_weight, void* q_out,
+                     int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head, int n_kv_head, int dim, int vdim, int padded,
+                     int page_size, int norm, float eps, void* stream);
+/* out[t, h * vdim + c] = f(o[t, h * o_head + c]) * gain[h * vdim + c] * act(g[t, h * vdim + c]); with `norm`, f divides a head's vdim values
+ * by their root mean square; gain may be null; act 0 sigmoid, 1 silu; g float. */
+int lb_head_gate(int in_dtype, int out_dtype, const void* o, int64_t ldo, int o_head, const float* g, int64_t ldg, const float* gain, void* out,
+                 int64_t ld_out, int n_tokens, int n_head, int vdim, int norm, int act, float eps, void* stream);
+/* mid[r, c] = act(gu[r, c]) * gu[r, inner + c]; act 0 sigmoid, 1 silu, 2 GELU (tanh form). */
+int lb_gated_act(int out_dtype, const float* gu, int64_t ld, void* mid, int64_t ldm, int n_rows, int inner, int act, void* stream);
+
+/* A matrix memory per head carried from row to row of every request: S = keep S + take k v^T, out = S^T q (see matrix_memory.cu).
+ * q, k, v (and the gates' pre-activations zi, zf, one column a head) are columns of float rows `ld` apart; either `decay` [n_head]
+ * (keep = decay, take = 1) or zi and zf with `cap`.  freq [rot_dims / 2] rotates the first rot_dims values of queries and keys.
+ * state: [slot][n_head][tiles][dim * value_tile + dim + 1] floats, slot_stride floats a slot; tiles = ceil(vdim / value_tile).
+ * chunked != 0: rows in pieces (prompt portions); 0: row by row. */
+int lb_matrix_memory(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay, const float* freq,
+                     int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, int64_t slot_stride, float* out,
+                     int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale, float k_scale, float cap, int chunked,
+                     void* stream);
+
+/* Routed experts (see routed_experts.cu).  ids and weights: [rows, top]. */
+int lb_router_topk(int dtype, const void* h, int64_t ldh, const void* router, int32_t* ids, float* weights, int n_rows, int n_experts, int width, int top,
+                   int softmax, int renormalise, void* stream);
+int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at, void* stream);
+/* gated: mid[place, :n] = act(W_e[:n] . a) * (W_e[n:2n] . a) with a = weights[pair] * h[pair / top]; else y[place, :n] = W_e . mid[place] (float). */
+int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
+                      const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top, int act,
+                      void* stream);
+int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, int n_rows, int width, int top, void* stream);
 
 #ifdef __cplusplus
 }

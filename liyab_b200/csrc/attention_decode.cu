@@ -72,7 +72,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
     const int sub = lane % TPK, kgroup = lane / TPK;
     const int page_size = 1 << page_shift;
     const int pos = positions[seq];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = lb_first_visible(pos, window);
     const int n_keys = pos + 1 - first;
     const int chunk = (n_keys + n_splits - 1) / n_splits;
     const int begin = first + split * chunk;

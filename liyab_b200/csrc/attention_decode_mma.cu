@@ -100,7 +100,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     const int page_size = 1 << page_shift;
     const size_t plane = (size_t)n_kv_head * page_size * HD;
     const int pos = positions[seq];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = lb_first_visible(pos, window);
     const int n_keys = pos + 1 - first;
     const int chunk = (n_keys + n_splits - 1) / n_splits;
     const int begin = first + split * chunk, end = min(pos + 1, begin + chunk);

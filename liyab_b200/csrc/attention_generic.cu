@@ -124,7 +124,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
 
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = lb_first_visible(pos, window);
     for (int j0 = first + warp * kTile; j0 <= pos; j0 += n_warps * kTile) {
         const int n_keys = min(kTile, pos + 1 - j0);
         // Each lane resolves its own key's row once; the others fetch it by shuffle.
@@ -247,7 +247,7 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
     const PieceWalk walk{lane / quads, lane % quads, 32 / quads, 32 % quads, quads};
 
     const size_t plane = (size_t)n_kv_head * page_size * head_dim;
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = lb_first_visible(pos, window);
     const int step = n_warps * kTile;
     auto row_of = [&](int j0) -> long long {      // this lane's key of the tile that starts at j0
         const int j = j0 + lane;

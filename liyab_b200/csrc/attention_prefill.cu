@@ -99,7 +99,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
 
     const int rows_here = min(kBM, q_len - tile_q * kBM);
     const int p_min = past + tile_q * kBM, p_max = p_min + rows_here - 1;
-    const int kv_lo = (window > 0 ? max(0, p_min - window + 1) : 0) / kBN * kBN;
+    const int kv_lo = lb_first_visible(p_min, window) / kBN * kBN;
     const int n_tiles = (p_max - kv_lo) / kBN + 1;
 
     // Q tile -> shared memory (rows past the portion's end are zeros).
@@ -134,7 +134,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
     const int pos_lo = past + tile_q * kBM + min(r_lo, rows_here - 1);
     const int pos_hi = past + tile_q * kBM + min(r_hi, rows_here - 1);
-    const int first_lo = window > 0 ? pos_lo - window + 1 : 0, first_hi = window > 0 ? pos_hi - window + 1 : 0;
+    const int first_lo = lb_first_visible(pos_lo, window), first_hi = lb_first_visible(pos_hi, window);
 
     uint32_t qf[KS][4];
     float o[OT][4];
@@ -175,7 +175,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
         }
         // Scale, mask what the rows cannot see, and update the running softmax.
         const int j0 = kv_lo + tile * kBN;
-        const bool need_mask = (j0 + kBN - 1 > p_min) || (window > 0 && j0 < p_max - window + 1);
+        const bool need_mask = (j0 + kBN - 1 > p_min) || (window != 0 && j0 < lb_first_visible(p_max, window));
         float mx_lo = -CUDART_INF_F, mx_hi = -CUDART_INF_F;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {

@@ -129,7 +129,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int page_size = 1 << page_shift;
     const int rows_here = min(kBM, q_len - tile_q * kBM);
     const int p_min = past + tile_q * kBM, p_max = p_min + rows_here - 1;
-    const int kv_lo = (window > 0 ? max(0, p_min - window + 1) : 0) / kBN * kBN;
+    const int kv_lo = lb_first_visible(p_min, window) / kBN * kBN;
     const int n_tiles = (p_max - kv_lo) / kBN + 1;
 
     if (threadIdx.x == 0) {
@@ -253,7 +253,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int r = quarter * 32 + lane;                              // row of the tile = lane of tensor memory
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int pos = past + tile_q * kBM + min(r, rows_here - 1);    // rows past the end copy the last one; not stored
-        const int first = window > 0 ? pos - window + 1 : 0;
+        const int first = lb_first_visible(pos, window);
         const float sc = scale * kLog2e;
         const uint32_t swz = (uint32_t)(r & 7);
         uint8_t* p_row = p_s + (size_t)r * 128;
@@ -265,7 +265,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) give_up(c, status, 6);
             tc_fence_after();
             const int j0 = kv_lo + tile * kBN + part * 32;             // this thread's first key of the tile
-            const bool need_mask = (j0 + 31 > p_min) || (window > 0 && j0 < p_max - window + 1);
+            const bool need_mask = (j0 + 31 > p_min) || (window != 0 && j0 < lb_first_visible(p_max, window));
             const uint32_t s_row = t_row + (uint32_t)(sb * kBN + part * 32);
             // First pass: the maximum of this part of the row; the parts meet in shared memory.
             float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;

@@ -101,6 +101,14 @@ inline cudaError_t lb_launch_overlapped_kind(int kind, void (*kernel)(Params...)
     return lb_launch_overlapped_cluster(kind, 1, kernel, grid, block, smem, stream, args...);
 }
 
+// The first key that the query at position `pos` sees.  `window` says which earlier keys are visible: 0 all of them; w > 0 the w
+// latest (pos - w + 1 .. pos); w < 0 those of the query's own chunk of -w positions, chunks counted from position 0 of the sequence.
+__host__ __device__ __forceinline__ int lb_first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos / (-window) * (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float lb_to_float(float v) { return v; }
 __device__ __forceinline__ float lb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -1,0 +1,304 @@
+// A feed-forward of many small experts of which every row uses a few.
+//
+//   lb_router_topk     z = router . h in 32-bit, score = sigmoid(z) (or the softmax over the experts), the `top` largest
+//                      per row (ties to the lower expert), their scores as weights (optionally divided by their sum).
+//   lb_expert_plan     the (row, choice) pairs sorted by expert, stably: offsets per expert, the sorted place of every
+//                      pair and the pair at every place.  One block; nothing returns to the host.
+//   lb_expert_product  for every expert the product of its pairs' rows with its own matrix, in tiles of rows that never
+//                      span two experts.  Either the first half of an expert, mid = act(gate . a) * (up . a) with
+//                      a = weight * h[row] gathered through the plan, or the second, y = down . mid.  32-bit FMA sums with K
+//                      in ascending order, so a row's result does not depend on which other rows share its tile.
+//   lb_expert_combine  x[row] += the sum of its pairs' results, in the order of its choices.
+#include "api.h"
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+__device__ __forceinline__ float lb_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------- router
+template <typename T>
+__global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ router, int32_t* __restrict__ ids,
+                                   float* __restrict__ weights, int E, int width, int top, int softmax, int renormalise) {
+    extern __shared__ float z[];       // [E]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const T* row = h + (size_t)t * ldh;
+    for (int e = warp; e < E; e += n_warps) {
+        const T* w = router + (size_t)e * width;
+        float acc = 0.0f;
+        for (int c = lane; c < width; c += 32) acc = fmaf(lb_to_float(row[c]), lb_to_float(w[c]), acc);
+        acc = lb_warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float zmax = -CUDART_INF_F, zsum = 0.0f;
+    if (softmax) {
+        for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
+        for (int e = 0; e < E; ++e) zsum += expf(z[e] - zmax);
+    }
+    float total = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        int best = 0;
+        for (int e = 1; e < E; ++e)
+            if (z[e] > z[best]) best = e;
+        const float s = softmax ? expf(z[best] - zmax) / zsum : lb_sigmoid(z[best]);
+        ids[(size_t)t * top + k] = best;
+        weights[(size_t)t * top + k] = s;
+        total += s;
+        z[best] = -CUDART_INF_F;
+    }
+    if (renormalise)
+        for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] /= total;
+}
+
+// ---------------------------------------------------------------- plan
+// offsets [E + 1]; place[pair] = where the pair stands in the sorted order; pair_at[place] = the pair.
+__global__ void __launch_bounds__(1024) expert_plan_kernel(const int32_t* __restrict__ ids, int n_pairs, int E, int32_t* __restrict__ offsets,
+                                                           int32_t* __restrict__ place, int32_t* __restrict__ pair_at) {
+    extern __shared__ int counts[];    // [E + 1]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += n_warps) {
+        int n = 0;
+        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+            const int p = p0 + lane;
+            n += __popc(__ballot_sync(0xffffffffu, p < n_pairs && ids[p] == e));
+        }
+        if (lane == 0) counts[e] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            const int n = counts[e];
+            counts[e] = at;
+            offsets[e] = at;
+            at += n;
+        }
+        counts[E] = at;
+        offsets[E] = at;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += n_warps) {
+        int at = counts[e];
+        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+            const int p = p0 + lane;
+            const bool mine = p < n_pairs && ids[p] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int where = at + __popc(mask & ((1u << lane) - 1u));
+                place[p] = where;
+                pair_at[where] = p;
+            }
+            at += __popc(mask);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- the experts' products
+struct ProductArgs {
+    const void* a;             // first half: the rows h [T, lda]; second half: mid [pairs, lda]
+    int64_t lda;
+    const void* w;             // [E][rows_per_expert][K]
+    int64_t expert_stride;     // elements between two experts' matrices
+    const int32_t* offsets;    // [E + 1]
+    const int32_t* pair_at;    // [pairs]
+    const float* weights;      // [pairs]
+    void* out;                 // first half: mid [pairs, ldo] of the element type; second: y [pairs, ldo] float
+    int64_t ldo;
+    int E, N, K, top, act;
+};
+
+constexpr int kBN = 64, kBK = 16;
+
+// 256 threads as 16 x 16; a thread makes TM x 4 results.  GATED: two matrices a tile (rows [0, N) gate, [N, 2N) up).
+template <typename T, int TM, bool GATED>
+__global__ void __launch_bounds__(256) expert_product_kernel(ProductArgs p) {
+    constexpr int BM = 16 * TM;
+    __shared__ float As[kBK][BM + 1];
+    __shared__ float Bs[GATED ? 2 : 1][kBK][kBN + 1];
+    __shared__ int tile_info[2];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, found = -1, first = 0;
+        for (int e = 0; e < p.E; ++e) {
+            const int n = p.offsets[e + 1] - p.offsets[e], tiles = (n + BM - 1) / BM;
+            if (tile < tiles) {
+                found = e;
+                first = p.offsets[e] + tile * BM;
+                break;
+            }
+            tile -= tiles;
+        }
+        tile_info[0] = found;
+        tile_info[1] = first;
+    }
+    __syncthreads();
+    const int e = tile_info[0];
+    if (e < 0) return;
+    const int r0 = tile_info[1], r_end = p.offsets[e + 1];
+    const int n0 = blockIdx.y * kBN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const T* W = static_cast<const T*>(p.w) + (size_t)e * p.expert_stride;
+    const T* A = static_cast<const T*>(p.a);
+
+    // What this thread stages: element (row ar, k ak) of the A tile, TM of them, and (feature bn, k bk) of the B tile, four.
+    float acc[TM][4], acc2[GATED ? TM : 1][4];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.0f;
+            if (GATED) acc2[i][j] = 0.0f;
+        }
+    const int ak = threadIdx.x & 15, ar0 = threadIdx.x >> 4;      // rows ar0 + 16 * i
+    const T* a_src[TM];
+    float a_scale[TM];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = r0 + ar0 + 16 * i;
+        a_src[i] = nullptr;
+        a_scale[i] = 1.0f;
+        if (r < r_end) {
+            if (GATED) {
+                const int pair = p.pair_at[r];
+                a_src[i] = A + (size_t)(pair / p.top) * p.lda;
+                a_scale[i] = p.weights[pair];
+            } else {
+                a_src[i] = A + (size_t)r * p.lda;
+            }
+        }
+    }
+    for (int k0 = 0; k0 < p.K; k0 += kBK) {
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int k = k0 + ak;
+            As[ak][ar0 + 16 * i] = (a_src[i] != nullptr && k < p.K) ? lb_to_float(a_src[i][k]) * a_scale[i] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = n0 + ar0 + 16 * i, k = k0 + ak;
+            const bool ok = n < p.N && k < p.K;
+            Bs[0][ak][ar0 + 16 * i] = ok ? lb_to_float(W[(size_t)n * p.K + k]) : 0.0f;
+            if (GATED) Bs[1][ak][ar0 + 16 * i] = ok ? lb_to_float(W[(size_t)(p.N + n) * p.K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kBK; ++kk) {
+            float av[TM], bv[4], bv2[4];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                bv[j] = Bs[0][kk][tx * 4 + j];
+                if (GATED) bv2[j] = Bs[1][kk][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                    if (GATED) acc2[i][j] = fmaf(av[i], bv2[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = r0 + ty * TM + i;
+        if (r >= r_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= p.N) continue;
+            if (GATED) {
+                const float g = acc[i][j];
+                const float z = p.act == 1 ? g * lb_sigmoid(g) : p.act == 2 ? lb_gelu_tanh(g) : lb_sigmoid(g);
+                static_cast<T*>(p.out)[(size_t)r * p.ldo + n] = lb_from_float<T>(z * acc2[i][j]);
+            } else {
+                static_cast<float*>(p.out)[(size_t)r * p.ldo + n] = acc[i][j];
+            }
+        }
+    }
+}
+
+__global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ place,
+                                      int n_rows, int width, int top) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const long total = (long)n_rows * width;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / width;
+        const int c = (int)(i - t * width);
+        float acc = 0.0f;
+        for (int k = 0; k < top; ++k) acc += y[(size_t)place[t * top + k] * ldy + c];
+        x[(size_t)t * ldx + c] += acc;
+    }
+}
+
+template <typename T, bool GATED>
+int launch_product(const ProductArgs& p, int n_pairs, cudaStream_t s) {
+    // Row tiles of 16 where the pairs are few (a decode step), of 64 otherwise; no more tiles than pairs / tile + experts.
+    const bool small = n_pairs <= 16 * p.E;
+    const int BM = small ? 16 : 64;
+    const int tiles = (n_pairs + BM - 1) / BM + min(p.E, n_pairs);
+    const dim3 grid((unsigned)tiles, (unsigned)((p.N + kBN - 1) / kBN)), block(256);
+    if (small) LB_CHECK_CUDA(lb_launch_overlapped(expert_product_kernel<T, 1, GATED>, grid, block, 0, s, p));
+    else LB_CHECK_CUDA(lb_launch_overlapped(expert_product_kernel<T, 4, GATED>, grid, block, 0, s, p));
+    return LB_OK;
+}
+
+}  // namespace
+
+extern "C" int lb_router_topk(int dtype, const void* h, int64_t ldh, const void* router, int32_t* ids, float* weights, int n_rows, int n_experts,
+                              int width, int top, int softmax, int renormalise, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && n_experts > 0 && width > 0 && top > 0 && top <= n_experts && n_experts <= 4096, "router: top %d of %d experts", top, n_experts);
+    if (n_rows == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)n_experts * sizeof(float);
+    if (dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<float>, dim3(n_rows), dim3(128), smem, s, (const float*)h, ldh, (const float*)router, ids, weights,
+                                           n_experts, width, top, softmax, renormalise));
+    else if (dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), smem, s, (const __nv_bfloat16*)h, ldh,
+                                           (const __nv_bfloat16*)router, ids, weights, n_experts, width, top, softmax, renormalise));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "router: unknown dtype %d", dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at, void* stream) {
+    LB_CHECK_ARG(n_pairs >= 0 && n_experts > 0 && n_experts <= 4096, "expert plan: bad sizes");
+    const int threads = 32 * max(1, min(32, n_experts));
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_plan_kernel, dim3(1), dim3(threads), (size_t)(n_experts + 1) * sizeof(int), static_cast<cudaStream_t>(stream), ids,
+                                       n_pairs, n_experts, offsets, place, pair_at));
+    return LB_OK;
+}
+
+extern "C" int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
+                                 const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top,
+                                 int act, void* stream) {
+    LB_CHECK_ARG(n_pairs >= 0 && n_experts > 0 && n > 0 && k > 0 && top > 0, "expert product: bad sizes");
+    if (n_pairs == 0) return LB_OK;
+    ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dtype == LB_F32) return gated ? launch_product<float, true>(p, n_pairs, s) : launch_product<float, false>(p, n_pairs, s);
+    if (dtype == LB_BF16) return gated ? launch_product<__nv_bfloat16, true>(p, n_pairs, s) : launch_product<__nv_bfloat16, false>(p, n_pairs, s);
+    return lb_fail(LB_ERR_INVALID_ARGUMENT, "expert product: unknown dtype %d", dtype);
+}
+
+extern "C" int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, int n_rows, int width, int top, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && width > 0 && top > 0, "expert combine: bad sizes");
+    if (n_rows == 0) return LB_OK;
+    const long total = (long)n_rows * width;
+    const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ldx, y, ldy, place, n_rows, width,
+                                       top));
+    return LB_OK;
+}

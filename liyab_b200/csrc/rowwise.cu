@@ -9,10 +9,11 @@ namespace {
 
 // ---------------------------------------------------------------- RMS norm in groups
 // The row is cut into `groups` equal consecutive parts; y = x / sqrt(mean(part^2) + eps) * w.  One block per
-// (row, group); the sum's order depends on the part's length alone.
+// (row, group); the sum's order depends on the part's length alone.  `gain_offset` is added to every gain (1 for gains
+// that are stored around zero, else 0).
 template <typename T>
 __global__ void rms_groups_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows, const float* __restrict__ w,
-                                  T* __restrict__ y, int64_t ldy, int part, float eps) {
+                                  T* __restrict__ y, int64_t ldy, int part, float eps, float gain_offset) {
     __shared__ float scratch[33];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -25,7 +26,7 @@ __global__ void rms_groups_kernel(const float* __restrict__ x, int64_t ldx, cons
     const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)part + eps);
     for (int i = threadIdx.x; i < part; i += blockDim.x) {
         float v = in[i] * inv;
-        if (gain != nullptr) v *= gain[i];
+        if (gain != nullptr) v *= gain[i] + gain_offset;
         out[i] = lb_from_float<T>(v);
     }
 }
@@ -309,15 +310,20 @@ int launch_token_side(float* x, int64_t ldx, const int32_t* tokens, const void* 
 
 extern "C" int lb_rms_groups(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, void* y, int64_t ldy,
                              int n_rows, int width, int groups, float eps, void* stream) {
+    return lb_rms_groups_offset(out_dtype, x, ldx, rows, weight, 0.0f, y, ldy, n_rows, width, groups, eps, stream);
+}
+
+extern "C" int lb_rms_groups_offset(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, float gain_offset, void* y,
+                                    int64_t ldy, int n_rows, int width, int groups, float eps, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && groups > 0 && width % groups == 0, "rms norm: %d values do not split into %d equal groups", width, groups);
     if (n_rows == 0) return LB_OK;
     const int part = width / groups, threads = part >= 1024 ? 256 : part >= 256 ? 128 : part > 32 ? 64 : 32;
     auto s = static_cast<cudaStream_t>(stream);
     if (out_dtype == LB_F32)
-        LB_CHECK_CUDA(lb_launch_overlapped(rms_groups_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, x, ldx, rows, weight, (float*)y, ldy, part, eps));
+        LB_CHECK_CUDA(lb_launch_overlapped(rms_groups_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, x, ldx, rows, weight, (float*)y, ldy, part, eps, gain_offset));
     else if (out_dtype == LB_BF16)
         LB_CHECK_CUDA(lb_launch_overlapped(rms_groups_kernel<__nv_bfloat16>, dim3(n_rows, groups), dim3(threads), 0, s, x, ldx, rows, weight,
-                                           (__nv_bfloat16*)y, ldy, part, eps));
+                                           (__nv_bfloat16*)y, ldy, part, eps, gain_offset));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "rms norm: unknown dtype %d", out_dtype);
     return LB_OK;
 }

@@ -55,6 +55,7 @@ private:
 
 void register_gpt2();      // gpt2.cpp
 void register_puzutar();   // puzutar.cpp
+void register_vosurax();   // vosurax.cpp
 
 void register_architecture(Architecture arch) { table()[arch.name] = std::move(arch); }
 
@@ -63,6 +64,7 @@ void register_builtin_architectures() {
     std::call_once(once, [] {
         register_gpt2();
         register_puzutar();
+        register_vosurax();
         register_architecture({"liyab_spec", {}, [](const Json& raw) { return std::make_unique<SpecConfig>(raw); }});
     });
     // Plug-ins named by the environment (paths separated by ':') are loaded once, so that the programs can run

@@ -1,5 +1,6 @@
 #include "builtin_parts.h"
 #include "parallel_parts.h"
+#include "gated_parts.h"
 
 #include <mutex>
 
@@ -36,6 +37,21 @@ void register_builtin_parts() {
         token_inputs().add("gated_side", {GatedTokenSide::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
                                               return std::make_shared<GatedTokenSide>(s, p);
                                           }});
+        mixers().add("gated_attention", {GatedAttention::parameters, [](const PartSpec& s, const Params& p, const Runtime& rt) {
+                                             return std::make_shared<GatedAttention>(s, p, rt);
+                                         }});
+        mixers().add("matrix_memory", {MatrixMemory::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                           return std::make_shared<MatrixMemory>(s, p);
+                                       }});
+        mixers().add("branch_sum", {BranchSum::parameters, [](const PartSpec& s, const Params& p, const Runtime& rt) {
+                                        return std::make_shared<BranchSum>(s, p, rt);
+                                    }});
+        feed_forwards().add("gated", {GatedFeedForward::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                          return std::make_shared<GatedFeedForward>(s, p);
+                                      }});
+        feed_forwards().add("routed", {RoutedExperts::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                           return std::make_shared<RoutedExperts>(s, p);
+                                       }});
         arrangements().add("parallel", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
                                return std::make_shared<ParallelBlock>(l, parts);
                            }});

@@ -106,6 +106,38 @@ public:
     int64_t max_;
 };
 
+// Chooses the attention kernel for queries q over a unit's pages.  bfloat16: a split-key decode kernel for steps of
+// single tokens (on the tensor cores where that one takes the shape, else scalar), the tensor-core prefill kernel for
+// steps with prompt portions, where they take the shape.  Else the generic kernel; all of the 32-bit engine runs on it,
+// so that there a position's result has the same bits however the work was cut.  `span`: the most keys a query sees.
+inline void attend(StepContext& ctx, const Rows& q, void* cache, const GroupView& view, const Rows& att, const kernels::AttentionShape& a, int span) {
+    const int T = ctx.n_tokens;
+    const int n_pages = view.group->pool.num_pages();
+    if (ctx.runtime.dtype == DType::BF16 && ctx.decode_only) {
+        const bool tensor = kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
+        if (tensor || scalar) {
+            const int splits = kernels::decode_splits(T, a.n_kv_head, span, tensor);
+            float* partial = nullptr;
+            int* counters = nullptr;
+            if (splits > 1) {
+                partial = static_cast<float*>(ctx.workspace->flat("attn.decode.partial",
+                                                                  static_cast<int64_t>(T) * a.n_head * splits * (a.head_dim + 2), DType::F32));
+                counters = static_cast<int*>(ctx.workspace->flat("attn.decode.counters", static_cast<int64_t>(T) * a.n_kv_head, DType::I32, true));
+            }
+            kernels::decode_attention(ctx.stream(), tensor, q, cache, n_pages, ctx.positions, view.block_table, view.table_width,
+                                      att, partial, counters, T, a, splits);
+            return;
+        }
+    }
+    if (ctx.runtime.dtype == DType::BF16 && kernels::prefill_supports(a)) {
+        kernels::prefill_attention(ctx.runtime, q, T, cache, n_pages, ctx.q_start, ctx.n_past, view.block_table, view.table_width,
+                                   att, ctx.n_seq, ctx.max_q_len, a);
+        return;
+    }
+    kernels::attention_generic(ctx.stream(), ctx.runtime.dtype, q, cache, ctx.tok_seq, ctx.positions, view.block_table,
+                               view.table_width, att, T, a);
+}
+
 // ---- causal self-attention over the paged cache, one fused projection of queries, keys and values -----
 // Sizes and constants are the spec's: heads, key/value heads, head size, the factor on the scores and the
 // window.  The step's keys and values are written to the unit's pages first; attention then reads every key,
@@ -194,41 +226,9 @@ private:
         const int T = ctx.n_tokens;
         const Rows q = qkv_out.columns(0, q_dim);
         const Rows att = ctx.workspace->get("attn.out", T, q_dim, ctx.runtime.dtype);
-        attend(ctx, q, cache, view, att, a);
+        attend(ctx, q, cache, view, att, a, ctx.max_positions);
         ctx.tap("attention", att);
         out.forward(ctx, att, x, T, kernels::kNone, &x);
-    }
-
-    // Chooses the attention kernel.  bfloat16: a split-key decode kernel for steps of single tokens (on the
-    // tensor cores where that one takes the shape, else scalar), the tensor-core prefill kernel for steps with
-    // prompt portions, where they take the shape.  Else the generic kernel; all of the 32-bit engine runs on it,
-    // so that there a position's result has the same bits however the work was cut.
-    void attend(StepContext& ctx, const Rows& q, void* cache, const GroupView& view, const Rows& att, const kernels::AttentionShape& a) {
-        const int T = ctx.n_tokens;
-        const int n_pages = view.group->pool.num_pages();
-        if (ctx.runtime.dtype == DType::BF16 && ctx.decode_only) {
-            const bool tensor = kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
-            if (tensor || scalar) {
-                const int splits = kernels::decode_splits(T, a.n_kv_head, ctx.max_positions, tensor);
-                float* partial = nullptr;
-                int* counters = nullptr;
-                if (splits > 1) {
-                    partial = static_cast<float*>(ctx.workspace->flat("attn.decode.partial",
-                                                                      static_cast<int64_t>(T) * a.n_head * splits * (a.head_dim + 2), DType::F32));
-                    counters = static_cast<int*>(ctx.workspace->flat("attn.decode.counters", static_cast<int64_t>(T) * a.n_kv_head, DType::I32, true));
-                }
-                kernels::decode_attention(ctx.stream(), tensor, q, cache, n_pages, ctx.positions, view.block_table, view.table_width,
-                                          att, partial, counters, T, a, splits);
-                return;
-            }
-        }
-        if (ctx.runtime.dtype == DType::BF16 && kernels::prefill_supports(a)) {
-            kernels::prefill_attention(ctx.runtime, q, T, cache, n_pages, ctx.q_start, ctx.n_past, view.block_table, view.table_width,
-                                       att, ctx.n_seq, ctx.max_q_len, a);
-            return;
-        }
-        kernels::attention_generic(ctx.stream(), ctx.runtime.dtype, q, cache, ctx.tok_seq, ctx.positions, view.block_table,
-                                   view.table_width, att, T, a);
     }
 
 public:
@@ -308,17 +308,22 @@ private:
 // `pre_norm`: x += mixer(norm(x)); x += feed_forward(norm(x)), the reference's run_block for this architecture
 // (src/core/transformer.cpp:5574-5577, 5633-5637, 5647, 5663-5666, 5684-5685, 5692).  The residual stream stays
 // float32 in every mode; the normalised input of a part is in the compute type.  Slots: mixer_norm (norm), mixer,
-// ff_norm (norm), feed_forward.
+// and, unless the block has no feed-forward, ff_norm (norm) and feed_forward.
 
 class PreNormBlock final : public Arrangement {
 public:
     PreNormBlock(const LayerSpec& spec, const LayerParts& parts)
-        : mixer_norm(parts.get<Norm>("mixer_norm")), mixer(parts.get<Mixer>("mixer")), ff_norm(parts.get<Norm>("ff_norm")),
-          feed_forward(parts.get<FeedForward>("feed_forward")), keep_(parts) {
-        if (spec.slots.size() != 4) throw invalid_model("arrangement 'pre_norm' takes the slots mixer_norm, mixer, ff_norm and feed_forward only");
+        : mixer_norm(parts.get<Norm>("mixer_norm")), mixer(parts.get<Mixer>("mixer")), keep_(parts) {
+        const bool with_ff = spec.find("feed_forward") != nullptr;
+        if (with_ff) {
+            ff_norm = &parts.get<Norm>("ff_norm");
+            feed_forward = &parts.get<FeedForward>("feed_forward");
+        }
+        if (spec.slots.size() != (with_ff ? 4u : 2u))
+            throw invalid_model("arrangement 'pre_norm' takes the slots mixer_norm and mixer, and ff_norm with feed_forward, only");
     }
     bool capturable() const override {
-        return mixer_norm.capturable() && mixer.capturable() && ff_norm.capturable() && feed_forward.capturable();
+        return mixer_norm.capturable() && mixer.capturable() && (feed_forward == nullptr || (ff_norm->capturable() && feed_forward->capturable()));
     }
     std::vector<Mixer*> mixers() const override { return {&mixer}; }
     void forward(StepContext& ctx, const Rows& x, CacheUnit unit) override {
@@ -336,21 +341,22 @@ public:
             mixer.forward(ctx, h, x, unit);
         }
         ctx.tap("mixer", x);
-        const std::optional<NormRecipe> second = ctx.tap_fn == nullptr ? ff_norm.recipe() : std::nullopt;
+        if (feed_forward == nullptr) return;
+        const std::optional<NormRecipe> second = ctx.tap_fn == nullptr ? ff_norm->recipe() : std::nullopt;
         ctx.phase(Phase::FeedForward);
-        if (!(second && feed_forward.forward_from(ctx, x, *second, x))) {
+        if (!(second && feed_forward->forward_from(ctx, x, *second, x))) {
             ctx.phase(Phase::Norm);
-            ff_norm.forward(ctx, x, h, T, nullptr);
+            ff_norm->forward(ctx, x, h, T, nullptr);
             ctx.tap("ff_norm", h);
             ctx.phase(Phase::FeedForward);
-            feed_forward.forward(ctx, h, x);
+            feed_forward->forward(ctx, h, x);
         }
         ctx.tap("feed_forward", x);
     }
     Norm& mixer_norm;
     Mixer& mixer;
-    Norm& ff_norm;
-    FeedForward& feed_forward;
+    Norm* ff_norm = nullptr;
+    FeedForward* feed_forward = nullptr;
 
 private:
     LayerParts keep_;

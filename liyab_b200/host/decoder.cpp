@@ -43,6 +43,7 @@ std::vector<ParamDecl> parameter_shapes(const ModelSpec& spec) {
     for (size_t i = 0; i < spec.layers.size(); ++i)
         for (const auto& slot : spec.layers[i].slots) add_decls(out, std::format("layers.{}.{}.", i, slot.name), slot_parameters(slot));
     add_decls(out, "final_norm.", norms().get(spec.final_norm.kind).parameters(spec.final_norm));
+    if (spec.pass_offsets > 0) out.push_back({"pass_offsets.weight", {spec.pass_offsets, spec.embedding.size}, ParamKind::Vector});
     if (!spec.head.tied) out.push_back({"head.weight", {spec.head.vocab_size, spec.head.size}, ParamKind::Matrix});
     if (spec.head.bias) out.push_back({"head.bias", {spec.head.vocab_size}, ParamKind::Vector});
     return out;
@@ -73,6 +74,7 @@ DecoderModel::DecoderModel(ModelSpec spec_, const Params& params, Runtime runtim
     final_norm = norms().get(spec.final_norm.kind).build(spec.final_norm, params_.sub("final_norm."), runtime);
     head_weight = spec.head.tied ? embedding : params_.at("head.weight");
     if (spec.head.bias) head_bias = static_cast<const float*>(params_.at("head.bias").data);
+    if (spec.pass_offsets > 0) pass_offsets = static_cast<const float*>(params_.at("pass_offsets.weight").data);
     const int n = static_cast<int>(spec.run_order.size());
     for (int i = 0; i < n; ++i) {
         const RunEntry& e = spec.run_order[static_cast<size_t>(i)];
@@ -81,6 +83,7 @@ DecoderModel::DecoderModel(ModelSpec spec_, const Params& params, Runtime runtim
         if (e.cache != i && spec.run_order[static_cast<size_t>(e.cache)].cache != e.cache)
             throw invalid_model("run order entry {} reads the cache of entry {}, which keeps none", i, e.cache);
         if (e.cache > i) throw invalid_model("run order entry {} reads the cache of a later entry {}", i, e.cache);
+        if (e.offset_row >= spec.pass_offsets) throw invalid_model("run order entry {} names pass offset {} of {}", i, e.offset_row, spec.pass_offsets);
     }
     kv_needs();      // checks that entries sharing a cache agree on its shape
 }
@@ -156,7 +159,12 @@ Rows DecoderModel::forward(StepContext& ctx) {
     ctx.tap("embed", x);
     for (size_t i = 0; i < spec.run_order.size(); ++i) {
         const RunEntry& e = spec.run_order[i];
+        if (e.offset_row >= 0) {
+            kernels::add_row(ctx.stream(), x, pass_offsets + static_cast<int64_t>(e.offset_row) * width, T);
+            ctx.tap("pass_offset", x);
+        }
         layers[static_cast<size_t>(e.layer)].block->forward(ctx, x, CacheUnit{e.cache, e.cache == static_cast<int>(i), static_cast<int>(i)});
+        ctx.tap("layer", x);
     }
     const int R = ctx.n_logit_rows;
     if (R == 0) return Rows{nullptr, DType::F32, 0, spec.vocab_size(), spec.vocab_size()};

@@ -38,6 +38,7 @@ public:
     std::shared_ptr<Norm> final_norm;
     Tensor head_weight;
     const float* head_bias = nullptr;
+    const float* pass_offsets = nullptr;      // [spec.pass_offsets, width] float32, or null
 
     // -- what the cache manager has to provide
     std::map<int, KvNeed> kv_needs() const;          // cache units (run-order entries that write keys and values)

@@ -38,13 +38,13 @@ std::unique_ptr<FusedDecodeStack> FusedDecodeStack::try_build(const DecoderModel
     std::vector<LayerRecord> records;
     for (size_t i = 0; i < spec.run_order.size(); ++i) {
         const RunEntry& e = spec.run_order[i];
-        if (e.cache != static_cast<int>(i)) return nullptr;
+        if (e.cache != static_cast<int>(i) || e.offset_row >= 0) return nullptr;
         const auto* block = dynamic_cast<const PreNormBlock*>(model.layers[static_cast<size_t>(e.layer)].block.get());
         if (block == nullptr) return nullptr;
         const auto* n1 = dynamic_cast<const LayerNorm*>(&block->mixer_norm);
-        const auto* n2 = dynamic_cast<const LayerNorm*>(&block->ff_norm);
+        const auto* n2 = dynamic_cast<const LayerNorm*>(block->ff_norm);
         const auto* at = dynamic_cast<const CausalSelfAttention*>(&block->mixer);
-        const auto* ff = dynamic_cast<const DenseFeedForward*>(&block->feed_forward);
+        const auto* ff = dynamic_cast<const DenseFeedForward*>(block->feed_forward);
         if (n1 == nullptr || n2 == nullptr || at == nullptr || ff == nullptr) return nullptr;
         const auto& a = at->shape;
         if ((a.head_dim != 64 && a.head_dim != 128) || (s->head_dim_ != 0 && s->head_dim_ != a.head_dim) || ff->inner % 8 != 0) return nullptr;

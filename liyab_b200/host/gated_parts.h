@@ -1,0 +1,421 @@
+// Parts of blocks whose mixers have gates, memories or several branches, and of feed-forwards with gates and routing:
+// attention with normalised queries and keys, a chunked or sliding mask and an output gate; a matrix memory per head
+// (fixed decay, or exponential gates with a running maximum); a mixer that sums several others, each over its own root
+// mean square; the gated feed-forward; and the feed-forward of routed experts with an optional shared one.  Every
+// size and constant is an option of the part's spec; none knows the model it is in.
+#pragma once
+
+#include <cmath>
+
+#include "builtin_parts.h"
+
+namespace liyab::builtin {
+
+// A short list of floats that lives on the device from the first step on (which is never a recorded one).
+class DeviceFloats {
+public:
+    std::vector<float> host;
+    const float* get(cudaStream_t s) {
+        if (dev_.data() == nullptr) {
+            dev_ = DeviceBuffer(std::max<size_t>(host.size(), 1) * sizeof(float), true);
+            if (!host.empty()) {
+                LIYAB_CUDA(cudaMemcpyAsync(dev_.data(), host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+                LIYAB_CUDA(cudaStreamSynchronize(s));
+            }
+        }
+        return static_cast<const float*>(dev_.data());
+    }
+
+private:
+    DeviceBuffer dev_;
+};
+
+// A bias for some of a fused projection's columns: [zeros .. | part | .. zeros] on the device, put together at the first step.
+class PartialBias {
+public:
+    void set(const float* part, int64_t at, int64_t count, int64_t total) { part_ = part; at_ = at; count_ = count; total_ = total; }
+    const float* get(cudaStream_t s) {
+        if (part_ == nullptr) return nullptr;
+        if (joined_.data() == nullptr) {
+            joined_ = DeviceBuffer(static_cast<size_t>(total_) * sizeof(float), true);
+            LIYAB_CUDA(cudaMemcpyAsync(static_cast<float*>(joined_.data()) + at_, part_, static_cast<size_t>(count_) * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            LIYAB_CUDA(cudaStreamSynchronize(s));
+        }
+        return static_cast<const float*>(joined_.data());
+    }
+
+private:
+    const float* part_ = nullptr;
+    int64_t at_ = 0, count_ = 0, total_ = 0;
+    DeviceBuffer joined_;
+};
+
+inline std::vector<float> rotation_frequencies(int dims, double base) {
+    std::vector<float> f;
+    for (int i = 0; i < dims / 2; ++i) f.push_back(static_cast<float>(std::pow(base, -2.0 * i / dims)));
+    return f;
+}
+
+// ---- attention with normalised queries and keys, a mask and an output gate --------------------------------
+// One projection makes [q (n_head x dim) | k (n_kv_head x dim) | v (n_kv_head x vdim) | g (n_head x vdim)] in 32-bit, with a
+// bias on q, k and v where the part has one.  With `qk_norm` every query and key head is divided by its root mean square
+// and multiplied by a gain of `dim` values shared by the heads.  score = (q . k) * scale over the keys that the mask
+// lets through: `window` w (the w latest) or `chunk` c (the earlier keys of the query's own chunk of c positions, chunks
+// counted from position 0 of the sequence), softmax, values; the heads are multiplied by gate(g) (`gate`: sigmoid, silu
+// or none) before the output projection.  No rotation: positions act through the mask alone.  dim and vdim may differ:
+// the cache and the attention kernels work on heads of `padded` values, the rest zeros, so the existing kernels serve.
+
+class GatedAttention final : public Mixer {
+public:
+    GatedAttention(const PartSpec& s, const Params& p, const Runtime& rt) {
+        hidden = need_int(s, "hidden");
+        H = static_cast<int>(need_int(s, "n_head"));
+        G = static_cast<int>(s.options.get_int("n_kv_head", H));
+        D = static_cast<int>(need_int(s, "dim"));
+        E = static_cast<int>(s.options.get_int("vdim", D));
+        if (G <= 0 || H % G != 0) throw invalid_model("gated_attention: n_head {} is not a multiple of n_kv_head {}", H, G);
+        shape.n_head = H;
+        shape.n_kv_head = G;
+        shape.head_dim = padded_head(std::max(D, E), rt.dtype);
+        shape.scale = static_cast<float>(s.options.get_number("scale", 1.0 / std::sqrt(static_cast<double>(D))));
+        shape.window = static_cast<int>(s.options.get_int("window", 0));
+        shape.chunk = static_cast<int>(s.options.get_int("chunk", 0));
+        if (shape.window < 0 || shape.chunk < 0 || (shape.window > 0 && shape.chunk > 0))
+            throw invalid_model("gated_attention: a window ({}) or a chunk ({}), not both, and neither negative", shape.window, shape.chunk);
+        qk_norm = s.options.get_bool("qk_norm", false);
+        eps = static_cast<float>(s.options.get_number("eps", 1e-6));
+        const std::string gate_name = s.options.get_string("gate", "none");
+        gate = gate_name == "none" ? -1 : kernels::gate_from_name(gate_name);
+        proj = Linear(p, "proj.", "gated_attention.proj");
+        out = Linear(p, "out.", "gated_attention.out");
+        if (const Tensor* b = p.find("qkv_bias")) bias.set(static_cast<const float*>(b->data), 0, qkv_cols(), proj.weight.dim(0));
+        if (qk_norm) {
+            q_gain = f32_or_null(&p.at("q_norm.weight"));
+            k_gain = f32_or_null(&p.at("k_norm.weight"));
+        }
+    }
+    static std::vector<ParamDecl> parameters(const PartSpec& s) {
+        const int64_t hidden = need_int(s, "hidden"), H = need_int(s, "n_head"), G = s.options.get_int("n_kv_head", H), D = need_int(s, "dim");
+        const int64_t E = s.options.get_int("vdim", D);
+        const bool gated = s.options.get_string("gate", "none") != "none";
+        std::vector<ParamDecl> out;
+        Linear::declare(out, "proj.", H * D + G * D + G * E + (gated ? H * E : 0), hidden, false);
+        if (s.options.get_bool("bias", false)) out.push_back({"qkv_bias", {H * D + G * D + G * E}, ParamKind::Vector});
+        if (s.options.get_bool("qk_norm", false)) {
+            out.push_back({"q_norm.weight", {D}, ParamKind::Vector});
+            out.push_back({"k_norm.weight", {D}, ParamKind::Vector});
+        }
+        Linear::declare(out, "out.", hidden, H * E, false);
+        return out;
+    }
+    // The head size the cache and the kernels work on: in bfloat16 the next size every tensor-core kernel takes, else a multiple of four.
+    static int padded_head(int n, DType dt) {
+        if (n > 256) throw unsupported("gated_attention: heads of {} values are more than the attention kernels take (256)", n);
+        if (dt == DType::BF16) {
+            int p = 16;
+            while (p < n) p *= 2;
+            return p;
+        }
+        return (n + 3) / 4 * 4;
+    }
+    bool capturable() const override { return true; }
+    std::optional<KvNeed> kv_need() const override { return KvNeed{G, shape.head_dim, shape.chunk > 0 ? shape.chunk : shape.window}; }
+
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, h, x, &x, unit); }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, h, y, nullptr, unit); }
+
+    kernels::AttentionShape shape;
+    int64_t hidden = 0;
+    int H = 0, G = 0, D = 0, E = 0, gate = -1;
+    bool qk_norm = false;
+    float eps = 1e-6f;
+    Linear proj, out;
+    const float* q_gain = nullptr;
+    const float* k_gain = nullptr;
+
+private:
+    int64_t qkv_cols() const { return static_cast<int64_t>(H) * D + static_cast<int64_t>(G) * (D + E); }
+    void run(StepContext& ctx, const Rows& h, const Rows& y, const Rows* residual, CacheUnit unit) {
+        const int T = ctx.n_tokens, P = shape.head_dim;
+        const DType dt = ctx.runtime.dtype;
+        Workspace& ws = *ctx.workspace;
+        cudaStream_t s = ctx.stream();
+        const Rows pr = ws.get("gated_attention.proj", T, proj.weight.dim(0), DType::F32);
+        kernels::linear(ctx.runtime, &ws, h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        const GroupView* view = nullptr;
+        void* cache = ctx.kv(unit.read, &view);
+        kernels::AttentionShape a = shape;
+        a.page_size = view->group->page_size;
+        const Rows q = ws.get("gated_attention.q", T, static_cast<int64_t>(H) * P, dt);
+        const kernels::QkvColumns cols{0, H * D, H * D + G * D, H, G, D, E, P, a.page_size};
+        kernels::qk_norm_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, qk_norm, eps);
+        ctx.tap("attention.q", q);
+        const Rows att = ws.get("gated_attention.att", T, static_cast<int64_t>(H) * P, dt);
+        const int reach = shape.chunk > 0 ? shape.chunk : shape.window;
+        attend(ctx, q, cache, *view, att, a, reach > 0 ? std::min(reach, ctx.max_positions) : ctx.max_positions);
+        const Rows heads = ws.get("gated_attention.heads", T, static_cast<int64_t>(H) * E, dt);
+        const Rows g = gate >= 0 ? pr.columns(qkv_cols(), static_cast<int64_t>(H) * E) : Rows{};
+        kernels::head_gate(s, att, P, g, nullptr, heads, T, H, E, false, std::max(gate, 0), eps);
+        ctx.tap("attention", heads);
+        kernels::linear(ctx.runtime, &ws, heads, out.weight, nullptr, y, T, kernels::kNone, residual);
+    }
+    PartialBias bias;
+};
+
+// ---- a matrix memory per head ----------------------------------------------------------------------------------
+// S_t = keep_t S_{t-1} + take_t k_t v_t^T, o_t = S_t^T q_t, per head, carried from token to token in the request's state slot
+// (32-bit).  `recurrence` "fixed_decay": keep = decay[head], take = 1 (retention).  `recurrence` "gated": two more numbers a head come
+// from the projection (with a bias), i = cap tanh(zi / cap) and f = logsigmoid(cap tanh(zf / cap)); with a running maximum m
+// that starts at 0, m_t = max(f + m_{t-1}, i), keep = exp(f + m_{t-1} - m_t), take = exp(i - m_t); n_t follows the same
+// recurrence with k alone and o_t is divided by max(|n_t . q_t|, exp(-m_t)) + 1e-6.  Queries and keys may be rotated (the first
+// rot_dims values of a head, value j with value j + rot_dims/2, angle position * rot_base^(-2j/rot_dims)) and scaled (q_scale,
+// k_scale, after the rotation).  Every head's o is divided by its root mean square (`head_norm`), times a gain over all heads'
+// values where the part has one (`norm_gain`), times gate(g), then the output projection.
+// One projection makes [q | k | v | g | zi | zf] in 32-bit.
+
+class MatrixMemory final : public Mixer {
+public:
+    MatrixMemory(const PartSpec& s, const Params& p) {
+        hidden = need_int(s, "hidden");
+        m.n_head = static_cast<int>(need_int(s, "n_head"));
+        m.dim = static_cast<int>(need_int(s, "dim"));
+        m.vdim = static_cast<int>(need_int(s, "vdim"));
+        m.value_tile = kernels::memory_value_tile(m.dim, m.vdim);
+        const std::string kind = s.options.get_string("recurrence", "fixed_decay");
+        if (kind != "fixed_decay" && kind != "gated") throw unsupported("matrix_memory: recurrence '{}' is not supported; supported: fixed_decay, gated", kind);
+        gated = kind == "gated";
+        if (gated) {
+            m.cap = static_cast<float>(s.options.get_number("gate_cap", 0.0));
+            if (!(m.cap > 0.0f)) throw invalid_model("matrix_memory: gate_cap must be positive");
+        } else {
+            const Json* d = s.options.find("decay");
+            if (d == nullptr || !d->is_array() || d->size() != static_cast<size_t>(m.n_head)) throw invalid_model("matrix_memory: 'decay' must list one number a head");
+            for (const auto& v : d->items()) decay.host.push_back(static_cast<float>(v.as_number()));
+        }
+        m.rot_dims = static_cast<int>(s.options.get_int("rot_dims", 0));
+        if (m.rot_dims < 0 || m.rot_dims > m.dim || m.rot_dims % 2 != 0) throw invalid_model("matrix_memory: {} of {} values cannot be rotated in pairs", m.rot_dims, m.dim);
+        freq.host = rotation_frequencies(m.rot_dims, s.options.get_number("rot_base", 10000.0));
+        m.q_scale = static_cast<float>(s.options.get_number("q_scale", 1.0));
+        m.k_scale = static_cast<float>(s.options.get_number("k_scale", 1.0));
+        head_norm = s.options.get_bool("head_norm", true);
+        eps = static_cast<float>(s.options.get_number("eps", 1e-6));
+        gate = kernels::gate_from_name(s.options.get_string("gate", "silu"));
+        proj = Linear(p, "proj.", "matrix_memory.proj");
+        out = Linear(p, "out.", "matrix_memory.out");
+        if (gated) bias.set(static_cast<const float*>(p.at("gate_bias").data), gate_at(), 2 * m.n_head, proj.weight.dim(0));
+        if (s.options.get_bool("norm_gain", false)) norm_gain = f32_or_null(&p.at("norm.weight"));
+    }
+    static std::vector<ParamDecl> parameters(const PartSpec& s) {
+        const int64_t hidden = need_int(s, "hidden"), H = need_int(s, "n_head"), D = need_int(s, "dim"), E = need_int(s, "vdim");
+        const bool gated = s.options.get_string("recurrence", "fixed_decay") == "gated";
+        std::vector<ParamDecl> out;
+        Linear::declare(out, "proj.", 2 * H * D + 2 * H * E + (gated ? 2 * H : 0), hidden, false);
+        if (gated) out.push_back({"gate_bias", {2 * H}, ParamKind::Vector});
+        if (s.options.get_bool("norm_gain", false)) out.push_back({"norm.weight", {H * E}, ParamKind::Vector});
+        Linear::declare(out, "out.", hidden, H * E, false);
+        return out;
+    }
+    bool capturable() const override { return true; }
+    std::optional<StateNeed> state_need() const override { return StateNeed{{m.slot_floats()}, DType::F32}; }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, h, x, &x, unit); }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, h, y, nullptr, unit); }
+
+    // Portions of this many rows or more go through the kernel that works in pieces.
+    static constexpr int kChunkedFrom = 16;
+    kernels::MemoryShape m;
+    int64_t hidden = 0;
+    bool gated = false, head_norm = true;
+    int gate = kernels::kSilu;
+    float eps = 1e-6f;
+    Linear proj, out;
+    const float* norm_gain = nullptr;
+
+private:
+    int64_t gate_at() const { return 2 * static_cast<int64_t>(m.n_head) * (m.dim + m.vdim); }
+    void run(StepContext& ctx, const Rows& h, const Rows& y, const Rows* residual, CacheUnit unit) {
+        if (!unit.write) throw invalid_model("matrix_memory: a memory is carried by the run that owns it; the run order lets another read it");
+        const int T = ctx.n_tokens, H = m.n_head, D = m.dim, E = m.vdim;
+        Workspace& ws = *ctx.workspace;
+        cudaStream_t s = ctx.stream();
+        const Rows pr = ws.get("matrix_memory.proj", T, proj.weight.dim(0), DType::F32);
+        kernels::linear(ctx.runtime, &ws, h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        const int64_t HD = static_cast<int64_t>(H) * D, HE = static_cast<int64_t>(H) * E;
+        const Rows q = pr.columns(0, HD), k = pr.columns(HD, HD), v = pr.columns(2 * HD, HE), g = pr.columns(2 * HD + HE, HE);
+        const Rows zi = pr.columns(gate_at(), H), zf = pr.columns(gate_at() + H, H);
+        const Rows o = ws.get("matrix_memory.o", T, HE, DType::F32);
+        kernels::matrix_memory(s, q, k, v, gated ? &zi : nullptr, gated ? &zf : nullptr, gated ? nullptr : decay.get(s), m.rot_dims > 0 ? freq.get(s) : nullptr,
+                               ctx.positions, ctx.q_start, ctx.state_slots, static_cast<float*>(ctx.state(unit.read)), o, ctx.n_seq, m,
+                               ctx.max_q_len >= kChunkedFrom);
+        ctx.tap("memory", o);
+        const Rows heads = ws.get("matrix_memory.heads", T, HE, ctx.runtime.dtype);
+        kernels::head_gate(s, o, E, g, norm_gain, heads, T, H, E, head_norm, gate, eps);
+        kernels::linear(ctx.runtime, &ws, heads, out.weight, nullptr, y, T, kernels::kNone, residual);
+    }
+    DeviceFloats decay, freq;
+    PartialBias bias;
+};
+
+// ---- several mixers side by side ----------------------------------------------------------------------------------
+// x += scale * sum_b rms(mixer_b(h)) * gain_b: every branch reads the same input, its output is divided by its root mean square
+// over the width and multiplied by its gain.  Options: `branches` [{"name", "part": {kind, options}}], `scale`, `eps`, `size`.
+// At most one branch may keep keys and values and at most one a state: both live under the block's one cache unit.
+
+class BranchSum final : public Mixer {
+public:
+    BranchSum(const PartSpec& s, const Params& p, const Runtime& rt) : size(need_int(s, "size")), scale(static_cast<float>(s.options.get_number("scale", 1.0))),
+                                                                       eps(static_cast<float>(s.options.get_number("eps", 1e-6))) {
+        for (const auto& [name, part] : branch_specs(s)) {
+            names.push_back(name);
+            branches.push_back(mixers().get(part.kind).build(part, p.sub(name + "."), rt));
+            gains.push_back(f32_or_null(&p.at(name + "_out.weight")));
+        }
+        int kv = 0, st = 0;
+        for (const auto& b : branches) {
+            kv += b->kv_need().has_value();
+            st += b->state_need().has_value();
+        }
+        if (kv > 1 || st > 1) throw unsupported("branch_sum: at most one branch with keys and values and one with a state");
+    }
+    static std::vector<std::pair<std::string, PartSpec>> branch_specs(const PartSpec& s) {
+        const Json* list = s.options.find("branches");
+        if (list == nullptr || !list->is_array() || list->size() == 0 || list->size() > 4) throw invalid_model("branch_sum: 'branches' must list one to four mixers");
+        std::vector<std::pair<std::string, PartSpec>> out;
+        for (const auto& b : list->items()) out.push_back({b.at("name").as_string(), PartSpec::from_json(b.at("part"), "branch_sum.branches")});
+        return out;
+    }
+    static std::vector<ParamDecl> parameters(const PartSpec& s) {
+        std::vector<ParamDecl> out;
+        for (const auto& [name, part] : branch_specs(s)) {
+            for (const auto& d : mixers().get(part.kind).parameters(part)) out.push_back({name + "." + d.name, d.shape, d.kind});
+            out.push_back({name + "_out.weight", {need_int(s, "size")}, ParamKind::Vector});
+        }
+        return out;
+    }
+    bool capturable() const override {
+        for (const auto& b : branches)
+            if (!b->capturable()) return false;
+        return true;
+    }
+    std::optional<KvNeed> kv_need() const override {
+        for (const auto& b : branches)
+            if (const auto n = b->kv_need()) return n;
+        return std::nullopt;
+    }
+    std::optional<StateNeed> state_need() const override {
+        for (const auto& b : branches)
+            if (const auto n = b->state_need()) return n;
+        return std::nullopt;
+    }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override {
+        std::vector<Rows> ys;
+        for (size_t i = 0; i < branches.size(); ++i) {
+            ys.push_back(ctx.workspace->get(std::format("branch_sum.{}", i), ctx.n_tokens, size, DType::F32));
+            branches[i]->forward_into(ctx, h, ys.back(), unit);
+            ctx.tap("branch." + names[i], ys.back());
+        }
+        kernels::rms_sum_add(ctx.stream(), x, ys, gains, ctx.n_tokens, scale, eps);
+    }
+    int64_t size;
+    float scale, eps;
+    std::vector<std::string> names;
+    std::vector<std::shared_ptr<Mixer>> branches;
+    std::vector<const float*> gains;
+};
+
+// ---- the gated feed-forward: down(gate(W_gate h) * (W_up h)) ------------------------------------------------------
+// One product makes [gate | up] in 32-bit, the gate's activation and the product of the halves are one pass, the second
+// product adds into the stream.  `activation`: silu, sigmoid or gelu_tanh.
+
+class GatedFeedForward final : public FeedForward {
+public:
+    GatedFeedForward(const PartSpec& s, const Params& p) : inner(need_int(s, "inner")), gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))) {
+        gate_up = Linear(p, "gate_up.", "gated.gate_up");
+        down = Linear(p, "down.", "gated.down");
+    }
+    static std::vector<ParamDecl> parameters(const PartSpec& s) {
+        const int64_t hidden = need_int(s, "hidden"), inner = need_int(s, "inner");
+        std::vector<ParamDecl> out;
+        Linear::declare(out, "gate_up.", 2 * inner, hidden, false);
+        Linear::declare(out, "down.", hidden, inner, false);
+        return out;
+    }
+    bool capturable() const override { return true; }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x) override {
+        const int T = ctx.n_tokens;
+        const Rows gu = ctx.workspace->get("gated.gate_up", T, 2 * inner, DType::F32);
+        gate_up.forward(ctx, h, gu, T);
+        const Rows mid = ctx.workspace->get("gated.inner", T, inner, ctx.runtime.dtype);
+        kernels::gated_act(ctx.stream(), gu, mid, T, gate);
+        down.forward(ctx, mid, x, T, kernels::kNone, &x);
+    }
+    int64_t inner;
+    int gate;
+    Linear gate_up, down;
+};
+
+// ---- routed experts --------------------------------------------------------------------------------------------------
+// z = router h in 32-bit; score = sigmoid(z) (`score` "sigmoid") or the softmax over the experts ("softmax"); every row goes to
+// its `top` experts with the largest scores, weights = their scores (divided by their sum with `renormalise`).  The weight
+// multiplies the expert's input: x += sum_e expert_e(w_e h), expert = down(gate(W_gate a) * (W_up a)) without biases.  With
+// `shared_inner` > 0 a gated feed-forward of that size runs for every row and is added.  The experts' matrices are stacked:
+// gate_up [experts x 2 inner, hidden] (per expert its gate rows, then its up rows) and down [experts x hidden, inner].
+
+class RoutedExperts final : public FeedForward {
+public:
+    RoutedExperts(const PartSpec& s, const Params& p)
+        : hidden(need_int(s, "hidden")), inner(need_int(s, "inner")), experts(static_cast<int>(need_int(s, "experts"))), top(static_cast<int>(need_int(s, "top"))),
+          gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))), renormalise(s.options.get_bool("renormalise", false)) {
+        if (top > experts) throw invalid_model("routed: top {} of {} experts", top, experts);
+        const std::string score = s.options.get_string("score", "sigmoid");
+        if (score != "sigmoid" && score != "softmax") throw unsupported("routed: score '{}' is not supported; supported: sigmoid, softmax", score);
+        softmax = score == "softmax";
+        if (s.options.get_string("weight_on", "input") != "input") throw unsupported("routed: the weight multiplies the expert's input; 'weight_on' knows 'input' only");
+        router = p.at("router.weight");
+        gate_up = p.at("experts.gate_up.weight");
+        down = p.at("experts.down.weight");
+        if (s.options.get_int("shared_inner", 0) > 0) shared = std::make_unique<GatedFeedForward>(shared_spec(s), p.sub("shared."));
+    }
+    static PartSpec shared_spec(const PartSpec& s) {
+        return {"gated", Json::object().set("hidden", need_int(s, "hidden")).set("inner", s.options.get_int("shared_inner", 0))
+                             .set("activation", s.options.get_string("shared_activation", s.options.get_string("activation", "silu")))};
+    }
+    static std::vector<ParamDecl> parameters(const PartSpec& s) {
+        const int64_t hidden = need_int(s, "hidden"), inner = need_int(s, "inner"), E = need_int(s, "experts");
+        std::vector<ParamDecl> out{{"router.weight", {E, hidden}, ParamKind::Matrix},
+                                   {"experts.gate_up.weight", {E * 2 * inner, hidden}, ParamKind::Matrix},
+                                   {"experts.down.weight", {E * hidden, inner}, ParamKind::Matrix}};
+        if (s.options.get_int("shared_inner", 0) > 0)
+            for (const auto& d : GatedFeedForward::parameters(shared_spec(s))) out.push_back({"shared." + d.name, d.shape, d.kind});
+        return out;
+    }
+    bool capturable() const override { return true; }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x) override {
+        const int T = ctx.n_tokens, pairs = T * top;
+        Workspace& ws = *ctx.workspace;
+        cudaStream_t s = ctx.stream();
+        // Per-row buffers hold `top` entries a row, so that they grow with the step's tokens as every other buffer does.
+        int32_t* ids = static_cast<int32_t*>(ws.get("routed.ids", T, top, DType::I32).data);
+        float* weights = ws.get("routed.weights", T, top, DType::F32).f32();
+        int32_t* place = static_cast<int32_t*>(ws.get("routed.place", T, top, DType::I32).data);
+        int32_t* pair_at = static_cast<int32_t*>(ws.get("routed.pair_at", T, top, DType::I32).data);
+        int32_t* offsets = static_cast<int32_t*>(ws.flat("routed.offsets", experts + 1, DType::I32));
+        kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise);
+        kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
+        Rows mid = ws.get("routed.inner", T, static_cast<int64_t>(top) * inner, ctx.runtime.dtype);
+        mid = Rows{mid.data, mid.dtype, static_cast<int64_t>(pairs), inner, inner};
+        Rows y = ws.get("routed.out", T, static_cast<int64_t>(top) * hidden, DType::F32);
+        y = Rows{y.data, y.dtype, static_cast<int64_t>(pairs), hidden, hidden};
+        kernels::expert_product(s, true, h, gate_up, experts, offsets, pair_at, weights, mid, pairs, static_cast<int>(inner), static_cast<int>(hidden), top, gate);
+        kernels::expert_product(s, false, mid, down, experts, offsets, pair_at, weights, y, pairs, static_cast<int>(hidden), static_cast<int>(inner), top, gate);
+        kernels::expert_combine(s, x, y, place, T, top);
+        ctx.tap("routed", x);
+        if (shared) shared->forward(ctx, h, x);
+    }
+    int64_t hidden, inner;
+    int experts, top, gate;
+    bool renormalise, softmax = false;
+    Tensor router, gate_up, down;
+    std::unique_ptr<GatedFeedForward> shared;
+};
+
+}  // namespace liyab::builtin

@@ -230,7 +230,7 @@ void attention_generic(cudaStream_t s, DType dtype, const Rows& q, const void* c
     if (q.dtype != dtype || out.dtype != dtype) throw invalid_argument("attention: q, cache and out must have one element type");
     check(lb_paged_attention_generic(code(dtype, "cache"), q.data, q.stride, cache, tok_seq, positions, block_table, table_width,
                                      out.data, out.stride, n_tokens, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale,
-                                     a.window, s), "paged_attention_generic");
+                                     a.mask(), s), "paged_attention_generic");
 }
 
 void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const void* cache, int n_pages, const int32_t* positions,
@@ -243,11 +243,11 @@ void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const vo
         throw invalid_argument("decode attention: scratch buffers are missing");
     if (tensor_cores)
         check(lb_decode_attention_mma(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
-                                      partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.window,
+                                      partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
                                       n_splits, s), "decode_attention_mma");
     else
         check(lb_decode_attention(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
-                                  counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.window, n_splits, s),
+                                  counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, s),
               "decode_attention");
 }
 
@@ -264,17 +264,103 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
     if (tc)
         check(lb_prefill_attention_tc(q.data, q.stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_width,
                                       out.data, out.stride, n_seq, max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size,
-                                      a.scale, a.window, rt.stream), "prefill_attention_tc");
+                                      a.scale, a.mask(), rt.stream), "prefill_attention_tc");
     else
         check(lb_prefill_attention(q.data, q.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_seq,
-                                   max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.window, rt.stream),
+                                   max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), rt.stream),
               "prefill_attention");
 }
 
-void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps) {
+void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps, float gain_offset) {
     if (x.dtype != DType::F32 || out.cols != x.cols || out.rows < n_rows) throw invalid_argument("rms norm: buffers must be [rows, width], the input float32");
-    check(lb_rms_groups(code(out.dtype, "out"), x.f32(), x.stride, rows, weight, out.data, out.stride, n_rows, static_cast<int>(x.cols), groups, eps, s),
-          "rms_groups");
+    check(lb_rms_groups_offset(code(out.dtype, "out"), x.f32(), x.stride, rows, weight, gain_offset, out.data, out.stride, n_rows, static_cast<int>(x.cols),
+                               groups, eps, s), "rms_groups");
+}
+
+void add_row(cudaStream_t s, const Rows& x, const float* v, int n_rows) {
+    if (x.dtype != DType::F32 || x.rows < n_rows) throw invalid_argument("add_row: the rows must be float32");
+    check(lb_add_row(x.f32(), x.stride, v, n_rows, static_cast<int>(x.cols), s), "add_row");
+}
+
+void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps) {
+    if (y.empty() || y.size() > 4 || weight.size() != y.size() || x.dtype != DType::F32) throw invalid_argument("rms_sum_add: one to four float branches with a weight each");
+    const float* ys[4];
+    int64_t ld[4];
+    for (size_t i = 0; i < y.size(); ++i) {
+        if (y[i].dtype != DType::F32 || y[i].cols != x.cols || y[i].rows < n_rows) throw invalid_argument("rms_sum_add: branch {} does not fit the rows", i);
+        ys[i] = y[i].f32();
+        ld[i] = y[i].stride;
+    }
+    check(lb_rms_sum_add(x.f32(), x.stride, static_cast<int>(y.size()), ys, ld, weight.data(), n_rows, static_cast<int>(x.cols), scale, eps, s), "rms_sum_add");
+}
+
+void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
+                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps) {
+    if (proj.dtype != DType::F32 || q_out.cols != static_cast<int64_t>(c.n_head) * c.padded) throw invalid_argument("qk_norm_store: buffers do not fit");
+    check(lb_qk_norm_store(code(q_out.dtype, "q_out"), proj.f32(), proj.stride, c.q_off, c.k_off, c.v_off, q_weight, k_weight, q_out.data, q_out.stride, cache,
+                           slot_mapping, n_tokens, c.n_head, c.n_kv_head, c.dim, c.vdim, c.padded, c.page_size, norm ? 1 : 0, eps, s), "qk_norm_store");
+}
+
+int gate_from_name(const std::string& name) {
+    if (name == "sigmoid") return kSigmoid;
+    if (name == "silu") return kSilu;
+    if (name == "gelu_tanh") return kGeluGate;
+    throw unsupported("gate '{}' is not supported; supported: sigmoid, silu, gelu_tanh", name);
+}
+
+void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const float* gain, const Rows& out, int n_tokens, int n_head, int vdim, bool norm,
+               int gate, float eps) {
+    if (out.cols != static_cast<int64_t>(n_head) * vdim || (g.data != nullptr && (g.dtype != DType::F32 || g.cols != out.cols))) throw invalid_argument("head_gate: buffers do not fit");
+    check(lb_head_gate(code(o.dtype, "o"), code(out.dtype, "out"), o.data, o.stride, o_head, g.f32(), g.stride, gain, out.data, out.stride, n_tokens, n_head,
+                       vdim, norm ? 1 : 0, gate, eps, s), "head_gate");
+}
+
+void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate) {
+    if (gu.dtype != DType::F32 || gu.cols != 2 * mid.cols) throw invalid_argument("gated_act: buffers do not fit");
+    check(lb_gated_act(code(mid.dtype, "mid"), gu.f32(), gu.stride, mid.data, mid.stride, n_rows, static_cast<int>(mid.cols), gate, s), "gated_act");
+}
+
+int memory_value_tile(int dim, int vdim) {
+    // Tiles of up to 64 value columns, equal in size; fewer columns where dim x tile floats would not fit a block's shared memory.
+    int cap = 64;
+    while (cap > 8 && static_cast<int64_t>(dim) * cap * 4 > 96 * 1024) cap /= 2;
+    const int tiles = (vdim + cap - 1) / cap;
+    return (vdim + tiles - 1) / tiles;
+}
+
+void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
+                   const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_seq, const MemoryShape& m,
+                   bool chunked) {
+    if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
+        (zf != nullptr && zf->stride != q.stride))
+        throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
+    check(lb_matrix_memory(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
+                           m.rot_dims, positions, q_start, slots, state, m.slot_floats(), out.f32(), out.stride, n_seq, m.n_head, m.dim, m.vdim,
+                           m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, s), "matrix_memory");
+}
+
+void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise) {
+    if (router.shape.size() != 2 || router.dim(1) != h.cols || router.dtype != h.dtype) throw invalid_argument("router: the matrix does not fit the rows");
+    check(lb_router_topk(code(h.dtype, "h"), h.data, h.stride, router.data, ids, weights, n_rows, static_cast<int>(router.dim(0)), static_cast<int>(h.cols), top,
+                         softmax ? 1 : 0, renormalise ? 1 : 0, s), "router_topk");
+}
+
+void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at) {
+    check(lb_expert_plan(ids, n_pairs, n_experts, offsets, place, pair_at, s), "expert_plan");
+}
+
+void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, int n_experts, const int32_t* offsets, const int32_t* pair_at,
+                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate) {
+    if (a.dtype != w.dtype || w.numel() != static_cast<int64_t>(n_experts) * (gated ? 2 : 1) * n * k || a.cols != k || out.cols != n)
+        throw invalid_argument("expert product: shapes do not fit");
+    if (out.dtype != (gated ? a.dtype : DType::F32)) throw invalid_argument("expert product: the output has the wrong type");
+    check(lb_expert_product(code(a.dtype, "a"), gated ? 1 : 0, a.data, a.stride, w.data, static_cast<int64_t>(gated ? 2 : 1) * n * k, offsets, pair_at, weights,
+                            out.data, out.stride, n_pairs, n_experts, n, k, top, gate, s), "expert_product");
+}
+
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top) {
+    if (x.dtype != DType::F32 || y.dtype != DType::F32 || x.cols != y.cols) throw invalid_argument("expert combine: buffers do not fit");
+    check(lb_expert_combine(x.f32(), x.stride, y.f32(), y.stride, place, n_rows, static_cast<int>(x.cols), top, s), "expert_combine");
 }
 
 void token_shift(cudaStream_t s, const Rows& h, const float* mix, const Rows& m, void* state, const ShiftLayout& l) {

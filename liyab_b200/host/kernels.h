@@ -11,6 +11,7 @@
 #include <atomic>
 #include <cstdint>
 #include <string>
+#include <vector>
 
 #include "device.h"
 #include "spec.h"
@@ -81,7 +82,10 @@ bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Te
 struct AttentionShape {
     int n_head = 0, n_kv_head = 0, head_dim = 0, page_size = 0;
     float scale = 1.0f;
-    int window = 0;
+    int window = 0;          // w > 0: a query sees the w latest keys
+    int chunk = 0;           // c > 0: a query sees the earlier keys of its own chunk of c positions, counted from position 0
+    // One number for the kernels: 0 all earlier keys, w > 0 a window, -c a chunk (a shape has one of the two at most).
+    int mask() const { return chunk > 0 ? -chunk : window; }
 };
 bool decode_scalar_supports(const AttentionShape& a);
 bool decode_mma_supports(const AttentionShape& a);
@@ -100,7 +104,8 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
 
 // ---- row-wise pieces between the products: RMS norm in groups, token shift, xIELU, gated side input ----
 // out[r] = x[rows ? rows[r] : r] cut into `groups` equal parts, each over its own root mean square, times weight.
-void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps);
+void rms_groups(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const Rows& out, int n_rows, int groups, float eps,
+                float gain_offset = 0.0f);      // gain_offset: added to every gain (1 for gains stored around zero)
 // The step's layout as the shift kernels need it.
 struct ShiftLayout {
     const int32_t* tok_seq = nullptr;
@@ -154,6 +159,48 @@ void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, c
                           int n_splits, bool merge = true);       // merge false: the parts are left for latent_finish
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
                       const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a);
+
+// ---- pieces around gated mixers and mixers of several branches ----
+// x[r, :] += v (float [width]) for the first n_rows rows.
+void add_row(cudaStream_t s, const Rows& x, const float* v, int n_rows);
+// x[r, :] += scale * sum_i rms(y_i[r, :]) * weight_i over up to four branches (float rows; a weight may be null).
+void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps);
+// Queries, keys and values of a float projection on their way to attention: per-head RMS norm of queries and keys (gains may be null),
+// queries into q_out [T, n_head * padded], keys and values into the cache pages (heads padded with zeros to `padded` values).
+struct QkvColumns {
+    int q_off = 0, k_off = 0, v_off = 0, n_head = 0, n_kv_head = 0, dim = 0, vdim = 0, padded = 0, page_size = 0;
+};
+void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
+                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps);
+enum Gate : int { kSigmoid = 0, kSilu = 1, kGeluGate = 2 };
+int gate_from_name(const std::string& name);
+// out[t, h * vdim + c] = f(o[t, h * o_head + c]) * gain * gate(g[t, h * vdim + c]); f: over the head's root mean square when `norm`;
+// rows g without data: no gate.
+void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const float* gain, const Rows& out, int n_tokens, int n_head, int vdim, bool norm,
+               int gate, float eps);
+// mid[r, c] = gate(gu[r, c]) * gu[r, inner + c]; gu float [rows, 2 * inner].
+void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate);
+
+// ---- a matrix memory per head, carried from token to token (retention with a fixed decay; gated with a running maximum) ----
+struct MemoryShape {
+    int n_head = 0, dim = 0, vdim = 0, value_tile = 0, rot_dims = 0;
+    float q_scale = 1.0f, k_scale = 1.0f, cap = 0.0f;
+    int tiles() const { return (vdim + value_tile - 1) / value_tile; }
+    int64_t slot_floats() const { return static_cast<int64_t>(n_head) * tiles() * (static_cast<int64_t>(dim) * value_tile + dim + 1); }
+};
+// The value tile a shape gets (the state's layout depends on it, so it is chosen once per part).
+int memory_value_tile(int dim, int vdim);
+// q, k, v, zi, zf: column blocks of one float buffer (same stride); decay [n_head] or the two gates.
+void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
+                   const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_seq, const MemoryShape& m,
+                   bool chunked);
+
+// ---- routed experts ----
+void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise);
+void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at);
+void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, int n_experts, const int32_t* offsets, const int32_t* pair_at,
+                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate);
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top);
 
 void sample(cudaStream_t s, const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
             const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids);

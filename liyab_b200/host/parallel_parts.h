@@ -12,23 +12,26 @@ namespace liyab::builtin {
 
 // ---- RMS norm in groups ------------------------------------------------------------------------------
 // The row is cut into `groups` equal consecutive parts; every part is divided by sqrt(mean(part^2) + eps), and the
-// whole row is multiplied by the gain.  groups = 1 is the plain RMS norm.  Statistics in 32-bit.
+// whole row is multiplied by the gain.  groups = 1 is the plain RMS norm.  Statistics in 32-bit.  With the option
+// `gain_offset` that number is added to every gain (1 for gains that are stored around zero).
 
 class GroupedRmsNorm final : public Norm {
 public:
     GroupedRmsNorm(const PartSpec& s, const Params& p)
-        : size(need_int(s, "size")), groups(static_cast<int>(s.options.get_int("groups", 1))), eps(static_cast<float>(s.options.get_number("eps", 1e-6))) {
+        : size(need_int(s, "size")), groups(static_cast<int>(s.options.get_int("groups", 1))), eps(static_cast<float>(s.options.get_number("eps", 1e-6))),
+          gain_offset(static_cast<float>(s.options.get_number("gain_offset", 0.0))) {
         if (groups < 1 || size % groups != 0) throw invalid_model("rms_norm: {} values do not split into {} equal groups", size, groups);
         weight = f32_or_null(&p.at("weight"));
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) { return {{"weight", {need_int(s, "size")}, ParamKind::Vector}}; }
     bool capturable() const override { return true; }
     void forward(StepContext& ctx, const Rows& x, const Rows& out, int n_rows, const int32_t* rows) override {
-        kernels::rms_groups(ctx.stream(), x, rows, weight, out, n_rows, groups, eps);
+        kernels::rms_groups(ctx.stream(), x, rows, weight, out, n_rows, groups, eps, gain_offset);
     }
     int64_t size;
     int groups;
     float eps;
+    float gain_offset;
     const float* weight = nullptr;
 };
 
@@ -48,7 +51,7 @@ public:
     }
     bool forward_normed(StepContext& ctx, const Rows& x, Norm& norm, const Rows& h, const Rows& m, void* state) override {
         const auto* rms = dynamic_cast<const GroupedRmsNorm*>(&norm);
-        if (rms == nullptr || rms->size != size) return false;
+        if (rms == nullptr || rms->size != size || rms->gain_offset != 0.0f) return false;
         kernels::rms_shift(ctx.stream(), x, rms->weight, weight, h, m, state, layout(ctx), rms->groups, rms->eps);
         return true;
     }

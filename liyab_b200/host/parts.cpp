@@ -42,6 +42,12 @@ void* StepContext::state(int unit, size_t* slot_bytes) const {
     return it->second.data();
 }
 
+void Mixer::forward_into(StepContext& ctx, const Rows& h, const Rows& out, CacheUnit unit) {
+    LIYAB_CUDA(cudaMemset2DAsync(out.data, static_cast<size_t>(out.stride) * dtype_size(out.dtype), 0, static_cast<size_t>(out.cols) * dtype_size(out.dtype),
+                                 static_cast<size_t>(ctx.n_tokens), ctx.stream()));
+    forward(ctx, h, out, unit);
+}
+
 const char* phase_name(Phase p) {
     static const char* names[] = {"embed", "norm", "mixer", "feed_forward", "head"};
     return names[static_cast<int>(p) % 5];

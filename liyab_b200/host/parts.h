@@ -166,6 +166,10 @@ public:
     virtual std::optional<StateNeed> state_need() const { return std::nullopt; }
     // Adds the mixer's output for the step's tokens to the residual stream x; `h` is its normalised input.
     virtual void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) = 0;
+    // Writes the mixer's output to `out` (float32 [T, width]) instead of adding it to the stream, for a mixer that is one of
+    // several branches.  By default `out` is cleared and `forward` adds into it; a mixer whose last product can write
+    // without a residual overrides this.
+    virtual void forward_into(StepContext& ctx, const Rows& h, const Rows& out, CacheUnit unit);
     // The same from the un-normalised rows `x_in` (float32) and the norm's recipe; false (and nothing done) where the
     // mixer cannot apply the recipe itself for this step.
     virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) { return false; }

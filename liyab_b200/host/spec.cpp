@@ -69,7 +69,12 @@ Json ModelSpec::to_json() const {
     }
     j.set("layers", ls);
     Json ro = Json::array();
-    for (const auto& e : run_order) ro.push(Json::object().set("layer", e.layer).set("cache", e.cache));
+    for (const auto& e : run_order) {
+        Json entry = Json::object().set("layer", e.layer).set("cache", e.cache);
+        if (e.offset_row >= 0) entry.set("offset_row", e.offset_row);
+        ro.push(entry);
+    }
+    if (pass_offsets > 0) j.set("pass_offsets", pass_offsets);
     j.set("run_order", ro);
     j.set("final_norm", final_norm.to_json());
     j.set("head", Json::object().set("vocab_size", head.vocab_size).set("size", head.size).set("tied", head.tied)
@@ -104,7 +109,8 @@ ModelSpec ModelSpec::from_json(const Json& j) {
             ++li;
         }
         for (const auto& r : j.at("run_order").items())
-            s.run_order.push_back({static_cast<int>(r.at("layer").as_int()), static_cast<int>(r.at("cache").as_int())});
+            s.run_order.push_back({static_cast<int>(r.at("layer").as_int()), static_cast<int>(r.at("cache").as_int()), static_cast<int>(r.get_int("offset_row", -1))});
+        s.pass_offsets = j.get_int("pass_offsets", 0);
         s.final_norm = PartSpec::from_json(j.at("final_norm"), "final_norm");
         const Json& h = j.at("head");
         s.head = {h.at("vocab_size").as_int(), h.at("size").as_int(), h.get_bool("tied", true), h.get_bool("bias", false),

@@ -60,9 +60,13 @@ struct LayerSpec {
 // this run of the layer reads; when it equals the entry's own index in the run
 // order the entry also writes that unit, otherwise it reads the keys and values
 // that the entry numbered `cache` wrote (and writes none of its own).
+// `offset_row` >= 0: before this run, row `offset_row` of the model's table of pass offsets
+// (ModelSpec::pass_offsets rows of the stream's width) is added to every row of the stream; a stretch of layers that
+// runs several times over the same weights tells its passes apart this way.
 struct RunEntry {
     int layer = 0;
     int cache = 0;
+    int offset_row = -1;
 };
 
 struct EmbeddingSpec {
@@ -92,6 +96,7 @@ struct ModelSpec {
     PartSpec final_norm;
     HeadSpec head;
     int64_t max_positions = 0;
+    int64_t pass_offsets = 0;            // rows of the parameter `pass_offsets.weight` (see RunEntry::offset_row); 0: none
     std::optional<int64_t> eos_token_id;
 
     int64_t vocab_size() const { return embedding.vocab_size; }
