@@ -164,7 +164,6 @@ Rows DecoderModel::forward(StepContext& ctx) {
             ctx.tap("pass_offset", x);
         }
         layers[static_cast<size_t>(e.layer)].block->forward(ctx, x, CacheUnit{e.cache, e.cache == static_cast<int>(i), static_cast<int>(i)});
-        ctx.tap("layer", x);
     }
     const int R = ctx.n_logit_rows;
     if (R == 0) return Rows{nullptr, DType::F32, 0, spec.vocab_size(), spec.vocab_size()};

@@ -113,6 +113,9 @@ def chunk_attention(h, W, p, m, eps, trace=None):
     return y @ W[p + "o"].T
 
 
+START_MAX = 0.0      # where the running maximum of a gated memory starts (tests move it to show that the start matters)
+
+
 def matrix_memory(h, W, p, m, eps, trace=None):
     """A matrix memory per head with exponential input gate and a running maximum that starts at 0."""
     n = h.shape[0]
@@ -124,7 +127,7 @@ def matrix_memory(h, W, p, m, eps, trace=None):
     gf = log_sigmoid(cap * np.tanh((h @ W[p + "f"].T + W[p + "f.b"]) / cap))
     o = np.zeros((n, H, E))
     for a in range(H):
-        S, z, mx = np.zeros((D, E)), np.zeros(D), 0.0
+        S, z, mx = np.zeros((D, E)), np.zeros(D), START_MAX
         for t in range(n):
             new = max(gf[t, a] + mx, gi[t, a])
             keep, take = math.exp(gf[t, a] + mx - new), math.exp(gi[t, a] - new)
@@ -169,6 +172,7 @@ def routed_ff(h, W, p, mlp, trace=None):
     if trace is not None:
         trace["experts"] = order
         trace["scores"] = s
+        trace["routed_only"] = y.copy()
     if mlp.get("shared"):
         y += gated_ff(h, W, p + "shared.")
     return y
@@ -208,7 +212,10 @@ def layer_forward(x, W, config, i, trace=None):
         if mlp["kind"] == "dense":
             x = x + dense_ff(h, W, p + "mlp.")
         elif mlp["kind"] == "moe":
-            x = x + routed_ff(h, W, p + "mlp.", mlp, trace)
+            y = routed_ff(h, W, p + "mlp.", mlp, trace)
+            if trace is not None:
+                trace["routed"] = x + trace.pop("routed_only")
+            x = x + y
         else:
             raise ValueError(mlp["kind"])
     return x
