@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--size small] [--layers L] [--dtype bfloat16]
     python bench.py --impl reference        # the reference's own tools on this machine's CPU, or why they cannot run
     python bench.py --design puzutar [--size small]   # Puzutar at GPT-2's layer sizes beside GPT-2 itself (see puzutar_line)
+    python bench.py --design vosurax [--size small]   # Vosurax likewise (see vosurax_line)
 
 A step is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (12 layers, width 768, 12 heads) with random weights, a batch of
@@ -286,6 +287,117 @@ def puzutar_line(args) -> int:
     return 0
 
 
+def vosurax_config(size, layers=0):
+    """Vosurax with the width, depth, head count, inner width and vocabulary of a GPT-2 size.  Of every four blocks the first is a
+    retention (heads of 64 query and 128 value values, half of them rotated, dense feed-forward), the others are attention in chunks
+    of 512 (heads of 64, a quarter as many key/value heads) beside a gated memory (half as many heads, 64 / 128 values) with 16
+    experts of a quarter of the inner width, two a token, and a shared one.  Blocks 1 and 2 run twice; two blocks fewer, so that the
+    runs equal GPT-2's layers."""
+    g = SIZES[size]
+    L, W, H = max(4, (layers or g["n_layer"]) - 2), g["n_embd"], g["n_head"]
+    blocks = []
+    for i in range(L):
+        if i % 4 == 0:
+            decay = [1.0 - 2.0 ** (-5 - 4 * h / H) for h in range(H)]
+            blocks.append(dict(type="retention", mixer=dict(heads=H, dim=64, vdim=128, decay=decay, rot=dict(base=1e6, dims=32)), mlp=dict(kind="dense", ff=g["n_inner"])))
+        else:
+            mixer = dict(left=dict(heads=H, kv_heads=max(1, H // 4), dim=64, vdim=64, scale=0.125, mask=dict(size=512)),
+                         right=dict(heads=max(1, H // 2), dim=64, vdim=128, gate_cap=15.0))
+            blocks.append(dict(type="parallel", mixer=mixer, mlp=dict(kind="moe", expert=dict(ff=g["n_inner"] // 4), router=dict(experts=16, top=2),
+                                                                      shared=dict(ff=g["n_inner"] // 4))))
+    return dict(architecture="Vosurax", vocab=g["vocab_size"], width=W, norm=dict(eps=1e-5), loop=dict(start=1, stop=3, times=2),
+                max_positions=g["n_positions"], layers=blocks)
+
+
+def vosurax_bytes_and_flops(cfg, dtype_bytes, batch):
+    """Bytes a decode step of `batch` requests must read (weights its rows touch, memories read and written, visible cache rows) and the
+    FLOPs of a prefill (products with the weights a token uses, attention inside its chunk, the memories' updates and reads)."""
+    W, V = cfg["width"], cfg["vocab"]
+    loop = cfg["loop"]
+    runs = [i for i in range(loop["start"])] + [i for _ in range(loop["times"]) for i in range(loop["start"], loop["stop"])] + list(range(loop["stop"], len(cfg["layers"])))
+    step_bytes, token_flops, attn, mem = 2 * V * W * dtype_bytes, 2 * V * W, [], []
+    for i in runs:
+        l = cfg["layers"][i]
+        m, mlp = l["mixer"], l["mlp"]
+        if l["type"] == "retention":
+            mats = W * m["heads"] * (2 * m["dim"] + 2 * m["vdim"]) + W * m["heads"] * m["vdim"]
+            mem.append((m["heads"], m["dim"], m["vdim"]))
+        else:
+            a, r = m["left"], m["right"]
+            mats = W * (a["heads"] * (a["dim"] + a["vdim"]) + a["kv_heads"] * (a["dim"] + a["vdim"])) + W * a["heads"] * a["vdim"]
+            mats += W * r["heads"] * (2 * r["dim"] + 2 * r["vdim"] + 2) + W * r["heads"] * r["vdim"]
+            mem.append((r["heads"], r["dim"], r["vdim"]))
+            attn.append((a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["mask"]["size"]))
+        used = mats
+        touched = mats
+        if mlp["kind"] == "dense":
+            used += 2 * W * mlp["ff"]
+            touched += 2 * W * mlp["ff"]
+        else:
+            E, top, F, S = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"], mlp["shared"]["ff"]
+            used += E * W + 3 * W * (top * F + S)
+            touched += E * W + 3 * W * S + 3 * W * F * E * (1.0 - (1.0 - top / E) ** batch)      # the experts a batch is expected to touch
+        token_flops += 2 * used
+        step_bytes += touched * dtype_bytes
+    state_bytes = sum(2 * 4 * H * (D * E + D + 1) for H, D, E in mem)
+    cache_row_bytes = [dtype_bytes * 2 * G * max(D, E) for _, G, D, E, _ in attn]
+
+    def decode_bytes(mean_context):
+        return step_bytes + batch * (state_bytes + sum(b * min(mean_context, c / 2) for b, (_, _, _, _, c) in zip(cache_row_bytes, attn)))
+
+    def prefill_flops(seq_lens, rows):
+        total = sum(seq_lens) * (token_flops - 2 * V * W) + 2 * rows * V * W
+        for H, G, D, E, c in attn:
+            total += sum(2 * H * (D + E) * sum(i % c + 1 for i in range(s)) for s in seq_lens)
+        for H, D, E in mem:
+            total += sum(seq_lens) * 4 * H * D * E
+        return total
+
+    return decode_bytes, prefill_flops
+
+
+def vosurax_line(args) -> int:
+    """--design vosurax: decode (batch 1 / 8 / 64, 512-token prompts) and prefill (2 x 1024 tokens) of Vosurax at the layer sizes of
+    GPT-2 `--size`, and the same four figures of GPT-2 at that size, device-timed by the library's own measurement."""
+    from liyab_b200.engine import Replayer
+    from liyab_b200.weights import write_random_model
+    pk = peaks()
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    cfg = vosurax_config(args.size, args.layers)
+    steps = min(args.steps, 128)
+    out = {"design": "vosurax", "size": args.size, "dtype": args.dtype, "peaks": pk["source"],
+           "config": {k: cfg[k] for k in ("width", "vocab", "norm", "loop")} | {"layers": len(cfg["layers"]), "retention": cfg["layers"][0], "parallel": cfg["layers"][1]}}
+    with tempfile.TemporaryDirectory(prefix="liyab_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "vosurax"), cfg, seed=0, dtype=args.dtype)
+        rep = Replayer(folder, args.dtype, max_tokens=64 * 1024, max_requests=64, cuda_graphs=True, max_step_tokens=PREFILL_TOKENS)
+        block = {}
+        for b in (1, 8, 64):
+            decode_bytes, flops = vosurax_bytes_and_flops(cfg, dtype_bytes, b)
+            r = rep.bench_decode(b, PROMPT_LEN, steps, 3, 0)
+            achieved = decode_bytes(r["mean_context"]) / (r["ms_per_step"] / 1e3) / 1e9
+            r.update(tok_s=b / (r["ms_per_step"] / 1e3), frac=achieved / pk["hbm_gbs"])
+            block[f"decode_b{b}"] = detail(r) | {"launches_per_step": r["kernel_launches"] // steps}
+        n_seq = PREFILL_TOKENS // 1024
+        r = rep.bench_prefill(n_seq, 1024, 5)
+        peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else FP32_TFLOPS_NOMINAL
+        block["prefill"] = {"value": round(PREFILL_TOKENS / (r["ms_per_step"] / 1e3), 1), "ms": round(r["ms_per_step"], 4),
+                            "frac": round(flops([1024] * n_seq, n_seq) / (r["ms_per_step"] / 1e3) / 1e12 / peak, 4), "launches": r["kernel_launches"]}
+        rep.close()
+        out["vosurax"] = block
+        if not args.layers:
+            out["gpt2"], _ = size_block(tmp, args.size, args.dtype, steps, pk)
+        else:
+            gpt = dict(SIZES[args.size], n_layer=args.layers)
+            gfolder = write_random_model(os.path.join(tmp, "gpt2"), gpt, seed=0, dtype=args.dtype)
+            grep_ = Replayer(gfolder, args.dtype, max_tokens=64 * 1024, max_requests=64, cuda_graphs=True, max_step_tokens=PREFILL_TOKENS)
+            gb = {f"decode_b{b}": detail(decode_point(grep_, gpt, dtype_bytes, b, steps, 3, pk)) for b in (1, 8, 64)}
+            gb["prefill"] = prefill_point(grep_, gpt, dtype_bytes, pk, args.dtype)
+            grep_.close()
+            out["gpt2"] = gb
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(args) -> int:
     from baseline.reference_arm import run
     return run(args)
@@ -303,13 +415,15 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="the headline figure only")
     ap.add_argument("--no-extra", action="store_true", help="skip the 32-bit engine, the other sizes and the mixed workload")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar"],
-                    help="puzutar: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar", "vosurax"],
+                    help="puzutar, vosurax: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     if args.design == "puzutar":
         return puzutar_line(args)
+    if args.design == "vosurax":
+        return vosurax_line(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (run with --gpus 1)")
         return 2

@@ -323,6 +323,8 @@ int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, int32_t* offs
 int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
                       const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top, int act,
                       void* stream);
+/* Non-zero: bfloat16 products stay on the 32-bit units instead of the tensor cores (for comparisons). */
+int lb_expert_product_set_plain(int on);
 int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, int n_rows, int width, int top, void* stream);
 
 #ifdef __cplusplus

@@ -229,6 +229,189 @@ __global__ void __launch_bounds__(256) expert_product_kernel(ProductArgs p) {
     }
 }
 
+// ---------------------------------------------------------------- the same products on the tensor cores (bfloat16)
+// 64 rows x 64 features a block, K in steps of 32, four warps of 16 rows each (`mma.sync m16n8k16`, 32-bit sums).  The weights'
+// tiles come by cp.async, the rows' through registers (the first half multiplies them by the pair's weight in 32-bit and rounds
+// once); two stages, so the next step's operands travel under this step's products.  Needs K, the rows' stride and the
+// experts' stride to be multiples of 8 elements and 16-byte aligned bases.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kMM = 64, kMN = 64, kMK = 32, kMLD = kMK + 8;
+
+template <bool GATED>
+__global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) {
+    using B16 = __nv_bfloat16;
+    __shared__ __align__(16) B16 As[2][kMM][kMLD];
+    __shared__ __align__(16) B16 Bs[2][GATED ? 2 : 1][kMN][kMLD];
+    __shared__ int tile_info[2];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, found = -1, first = 0;
+        for (int e = 0; e < p.E; ++e) {
+            const int n = p.offsets[e + 1] - p.offsets[e], tiles = (n + kMM - 1) / kMM;
+            if (tile < tiles) {
+                found = e;
+                first = p.offsets[e] + tile * kMM;
+                break;
+            }
+            tile -= tiles;
+        }
+        tile_info[0] = found;
+        tile_info[1] = first;
+    }
+    __syncthreads();
+    const int e = tile_info[0];
+    if (e < 0) return;
+    const int r0 = tile_info[1], r_end = p.offsets[e + 1];
+    const int n0 = blockIdx.y * kMN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const B16* W = static_cast<const B16*>(p.w) + (size_t)e * p.expert_stride;
+    const B16* A = static_cast<const B16*>(p.a);
+
+    // This thread's two 16-byte pieces of every A tile and of every B tile: piece v -> (row v / 4, elements (v % 4) * 8 ..).
+    const B16* a_src[2];
+    float a_scale[2];
+    const B16* b_src[2];
+    int piece_row[2], piece_k[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int v = threadIdx.x + 128 * i;
+        piece_row[i] = v >> 2;
+        piece_k[i] = (v & 3) * 8;
+        const int r = r0 + piece_row[i];
+        a_src[i] = nullptr;
+        a_scale[i] = 1.0f;
+        if (r < r_end) {
+            if (GATED) {
+                const int pair = p.pair_at[r];
+                a_src[i] = A + (size_t)(pair / p.top) * p.lda;
+                a_scale[i] = p.weights[pair];
+            } else {
+                a_src[i] = A + (size_t)r * p.lda;
+            }
+        }
+        const int n = n0 + piece_row[i];
+        b_src[i] = n < p.N ? W + (size_t)n * p.K : nullptr;
+    }
+    uint4 a_regs[2];
+    auto fetch_a = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int k = k0 + piece_k[i];
+            a_regs[i] = (a_src[i] != nullptr && k < p.K) ? *reinterpret_cast<const uint4*>(a_src[i] + k) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto store_a = [&](int stage) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint4 v = a_regs[i];
+            if (GATED) {
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h2[j]);
+                    h2[j] = __floats2bfloat162_rn(f.x * a_scale[i], f.y * a_scale[i]);
+                }
+            }
+            *reinterpret_cast<uint4*>(&As[stage][piece_row[i]][piece_k[i]]) = v;
+        }
+    };
+    auto fetch_b = [&](int k0, int stage) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int k = k0 + piece_k[i];
+            const bool ok = b_src[i] != nullptr && k < p.K;
+            cp_async16(&Bs[stage][0][piece_row[i]][piece_k[i]], ok ? b_src[i] + k : W, ok);
+            if (GATED) cp_async16(&Bs[stage][1][piece_row[i]][piece_k[i]], ok ? b_src[i] + (size_t)p.N * p.K + k : W, ok);
+        }
+        cp_async_commit();
+    };
+
+    float acc[8][4], acc2[GATED ? 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.0f;
+            if (GATED) acc2[i][j] = 0.0f;
+        }
+    const int steps = (p.K + kMK - 1) / kMK;
+    fetch_a(0);
+    fetch_b(0, 0);
+    store_a(0);
+    for (int it = 0; it < steps; ++it) {
+        const int stage = it & 1;
+        cp_async_wait_all();
+        __syncthreads();
+        const bool more = it + 1 < steps;
+        if (more) {
+            fetch_b((it + 1) * kMK, stage ^ 1);
+            fetch_a((it + 1) * kMK);
+        }
+        const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+        for (int kk = 0; kk < kMK / 16; ++kk) {
+            uint32_t af[4];
+            ldmatrix_x4(af, smem_addr(&As[stage][warp * 16 + (mat & 1) * 8 + r][kk * 16 + (mat >> 1) * 8]));
+#pragma unroll
+            for (int nt = 0; nt < 8; nt += 2) {
+                uint32_t b[4];
+                ldmatrix_x4(b, smem_addr(&Bs[stage][0][(nt + (mat >> 1)) * 8 + r][kk * 16 + (mat & 1) * 8]));
+                mma_bf16(acc[nt], af, b[0], b[1]);
+                mma_bf16(acc[nt + 1], af, b[2], b[3]);
+                if (GATED) {
+                    ldmatrix_x4(b, smem_addr(&Bs[stage][1][(nt + (mat >> 1)) * 8 + r][kk * 16 + (mat & 1) * 8]));
+                    mma_bf16(acc2[nt], af, b[0], b[1]);
+                    mma_bf16(acc2[nt + 1], af, b[2], b[3]);
+                }
+            }
+        }
+        if (more) store_a(stage ^ 1);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) {
+            const int row = r0 + warp * 16 + g + (e4 >= 2 ? 8 : 0), n = n0 + nt * 8 + 2 * t + (e4 & 1);
+            if (row >= r_end || n >= p.N) continue;
+            if (GATED) {
+                const float z = acc[nt][e4];
+                const float a = p.act == 1 ? z * lb_sigmoid(z) : p.act == 2 ? lb_gelu_tanh(z) : lb_sigmoid(z);
+                static_cast<B16*>(p.out)[(size_t)row * p.ldo + n] = __float2bfloat16_rn(a * acc2[nt][e4]);
+            } else {
+                static_cast<float*>(p.out)[(size_t)row * p.ldo + n] = acc[nt][e4];
+            }
+        }
+}
+
+template <bool GATED>
+int launch_product_mma(const ProductArgs& p, int n_pairs, cudaStream_t s) {
+    const int tiles = (n_pairs + kMM - 1) / kMM + min(p.E, n_pairs);
+    const dim3 grid((unsigned)tiles, (unsigned)((p.N + kMN - 1) / kMN)), block(128);
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_product_mma_kernel<GATED>, grid, block, 0, s, p));
+    return LB_OK;
+}
+
+bool mma_takes(const ProductArgs& p) {
+    return p.K % 8 == 0 && p.lda % 8 == 0 && p.expert_stride % 8 == 0 && ((uintptr_t)p.a & 15) == 0 && ((uintptr_t)p.w & 15) == 0;
+}
+
 __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ place,
                                       int n_rows, int width, int top) {
     lb_wait_for_predecessor();
@@ -281,6 +464,13 @@ extern "C" int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, in
     return LB_OK;
 }
 
+// Tests compare the two bfloat16 paths: non-zero keeps every product on the 32-bit units.
+static int lb_expert_product_plain_only = 0;
+extern "C" int lb_expert_product_set_plain(int on) {
+    lb_expert_product_plain_only = on;
+    return LB_OK;
+}
+
 extern "C" int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
                                  const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top,
                                  int act, void* stream) {
@@ -289,6 +479,8 @@ extern "C" int lb_expert_product(int dtype, int gated, const void* a, int64_t ld
     ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act};
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32) return gated ? launch_product<float, true>(p, n_pairs, s) : launch_product<float, false>(p, n_pairs, s);
+    if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only)
+        return gated ? launch_product_mma<true>(p, n_pairs, s) : launch_product_mma<false>(p, n_pairs, s);
     if (dtype == LB_BF16) return gated ? launch_product<__nv_bfloat16, true>(p, n_pairs, s) : launch_product<__nv_bfloat16, false>(p, n_pairs, s);
     return lb_fail(LB_ERR_INVALID_ARGUMENT, "expert product: unknown dtype %d", dtype);
 }

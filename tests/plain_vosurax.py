@@ -113,7 +113,8 @@ def chunk_attention(h, W, p, m, eps, trace=None):
     return y @ W[p + "o"].T
 
 
-START_MAX = 0.0      # where the running maximum of a gated memory starts (tests move it to show that the start matters)
+START_MAX = 0.0      # where the running maximum of a gated memory starts
+FLOOR = True         # whether exp(-m) bounds the gated memory's divisor from below (tests switch it off to show that it matters)
 
 
 def matrix_memory(h, W, p, m, eps, trace=None):
@@ -134,7 +135,7 @@ def matrix_memory(h, W, p, m, eps, trace=None):
             S = keep * S + take * np.outer(k[t, a], v[t, a])
             z = keep * z + take * k[t, a]
             mx = new
-            o[t, a] = (S.T @ q[t, a]) / (max(abs(float(z @ q[t, a])), math.exp(-mx)) + 1e-6)
+            o[t, a] = (S.T @ q[t, a]) / (max(abs(float(z @ q[t, a])), math.exp(-mx) if FLOOR else 0.0) + 1e-6)
     if trace is not None:
         trace["memory.heads"] = o.reshape(n, H * E)
     y = rms(o, eps).reshape(n, H * E) * W[p + "norm"] * sigmoid(h @ W[p + "g"].T)

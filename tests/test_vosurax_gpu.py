@@ -50,11 +50,12 @@ def make_engine(path, dtype, max_tokens, **options):
     return Replayer(path, dtype, max_tokens, **options)
 
 
-def check(got, want, dtype, rel_tol=REL_TOL):
+def check(got, want, dtype, rel_tol=REL_TOL, flips=True):
     """float32: every logit within rel_tol of the plain model's.  bfloat16: per row, the root mean square of the
-    difference (its mean taken off) over that of the sequence's logits; 8 bits of mantissa put it near a percent.
-    A rounding may send a row to another expert, so a few rows may lie further out: the mean is held to 2 %, 97 % of
-    the rows to 6 %."""
+    difference (its mean taken off) over that of the sequence's logits; 8 bits of mantissa put it near a percent, and the
+    mean is held to 2 %.  Where two experts' scores lie close, a rounding sends a row to another expert, and the memories
+    carry that difference to the positions after it (`flips`): then up to a tenth of the rows may lie beyond 6 %, none beyond
+    the logits' own spread.  Models whose routers decide by clear margins are held to 6 % in every row."""
     if dtype != "bfloat16":
         return tt.check_rows(got, want, rel_tol)
     errs = []
@@ -64,7 +65,10 @@ def check(got, want, dtype, rel_tol=REL_TOL):
         errs.append(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((spread ** 2).mean()))
     errs = np.asarray(errs)
     assert np.isfinite(errs).all() and errs.mean() <= 2e-2, f"mean relative error {errs.mean():.3e}"
-    assert (errs > 6e-2).mean() <= 0.03, f"{(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %"
+    if flips:
+        assert (errs > 6e-2).mean() <= 0.10 and errs.max() < 1.0, f"{(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %, the worst by {errs.max():.2f}"
+    else:
+        assert errs.max() <= 6e-2, f"{(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %"
     return {"mean": float(errs.mean()), "worst": float(errs.max())}
 
 
@@ -230,8 +234,9 @@ def test_memories_reach_far_back(kind, tmp_path):
 
 
 def test_first_tokens_of_a_sequence(tmp_path):
-    """Input gates far below zero at a sequence's start: the running maximum stays at its starting value 0 for a while, and a
-    memory whose maximum started at minus infinity would answer differently (shown on the plain model)."""
+    """Input gates far below zero at a sequence's start: the running maximum stays near its starting value 0, little has been taken
+    into the memory, and what divides the read-out is the floor exp(-m), not |n . q|.  Without the floor the plain model answers
+    clearly differently, so a floor that is left out, or a maximum or a state that does not start at zero, shows."""
     config = dict(architecture="Vosurax", vocab=50, width=32, norm=dict(eps=1e-5), layers=[layer(side_by_side(1, 1, 4, 4, 0.5, 8, 2, 8, 12, 14.0), dense(40))])
     weights = random_weights(config, 8)
     weights["l0.mix.right.i.b"] = weights["l0.mix.right.i.b"] * 0.0 - 6.0
@@ -239,12 +244,12 @@ def test_first_tokens_of_a_sequence(tmp_path):
     path = write_model(str(tmp_path / "first"), config, weights)
     toks = np.random.default_rng(3).integers(0, 50, size=40).astype(int).tolist()
     want = plain.forward(config, weights, toks)
-    plain.START_MAX = -np.inf
+    plain.FLOOR = False
     try:
         other = plain.forward(config, weights, toks)
     finally:
-        plain.START_MAX = 0.0
-    assert (np.abs(other - want).max(axis=1) / np.abs(want).max() > 1e-2).sum() >= 5, "the weights do not show where the maximum starts"
+        plain.FLOOR = True
+    assert (np.abs(other - want).max(axis=1) / np.abs(want).max() > 1e-2).sum() >= 5, "the weights do not show the divisor's floor"
     reqs = {"a": toks}
     for steps in (tt.whole(reqs), tt.tail_one_by_one(reqs, 10 ** 6), tt.changing_portions(reqs, sizes=(2, 3, 2, 17))):
         got = tt.collect(make_engine(path, "float32", max_tokens=64), steps)
@@ -258,8 +263,13 @@ def test_sharp_router_and_weight_on_the_input(tmp_path):
         layer(retention(2, 8, 8, [0.9, 0.8], 4), moe(7, 3, 24, 0)), layer(retention(1, 8, 8, [0.9], 0), moe(5, 1, 16, 8))])
     weights = random_weights(config, 12, router_std=12.0)
     path = write_model(str(tmp_path / "router"), config, weights)
-    toks = np.random.default_rng(4).integers(0, 60, size=90).astype(int).tolist()
-    want = plain.forward(config, weights, toks)
+    toks = np.random.default_rng(27).integers(0, 60, size=48).astype(int).tolist()
+    traces = []
+    want = plain.forward(config, weights, toks, traces=traces)
+    for trace, l in zip(traces, config["layers"]):       # the last chosen expert and the best unchosen one are clearly apart
+        sc, top = trace["scores"], l["mlp"]["router"]["top"]
+        z = -np.sort(-(np.log(sc) - np.log1p(-sc)), axis=1)
+        assert np.nanmin(z[:, top - 1] - z[:, top]) > 0.3, "the router's margins are not clear"
     real = plain.routed_ff
 
     def weight_on_output(h, W, p, mlp, trace=None):
@@ -278,8 +288,8 @@ def test_sharp_router_and_weight_on_the_input(tmp_path):
         plain.routed_ff = real
     assert np.abs(other - want).max() / np.abs(want).max() > 1e-2
     for dtype in ("float32", "bfloat16"):
-        for steps in (tt.whole({"a": toks}), tt.changing_portions({"a": toks}, sizes=(40, 1, 2, 9))):
-            check(tt.collect(make_engine(path, dtype, max_tokens=128), steps), {"a": want}, dtype)
+        for steps in (tt.whole({"a": toks}), tt.changing_portions({"a": toks}, sizes=(20, 1, 2, 9))):
+            check(tt.collect(make_engine(path, dtype, max_tokens=128), steps), {"a": want}, dtype, flips=False)
 
 
 def test_long_decoding_reuses_pages(models):
