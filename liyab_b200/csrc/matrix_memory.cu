@@ -14,9 +14,9 @@
 // keeps its own n and m, so that the blocks of a launch share nothing.
 //
 // lb_matrix_memory walks a request's rows one after the other (a block per (request, head, value tile)); a decode step
-// is one such row.  lb_matrix_memory_chunks does the same in pieces of 32 rows: inside a piece the rows' sums are
-// products of small matrices (scores q_t . k_j weighted by the decay between j and t, then the values), and the state
-// moves once per piece.
+// is one such row.  With `chunked` it does the same in pieces of 32 rows: inside a piece the rows' sums are products of
+// small matrices (scores q_t . k_j weighted by the decay between j and t, then the values), and the state moves once per
+// piece.
 #include "api.h"
 #include "common.cuh"
 
@@ -139,6 +139,179 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
     if (threadIdx.x == 0) st[(size_t)D * VT + D] = m;
 }
 
+// ---------------------------------------------------------------- in pieces of 32 rows
+// With b_t the sum of the log forget gates from the piece's start to row t, and m_t the running maximum (by the same recursion
+// as row by row):  w(t, j) = exp(i_j + b_t - b_j - m_t) for j <= t,  alpha_t = exp(b_t + m_prev - m_t),
+//     o_t = alpha_t S_prev^T q_t + sum_{j <= t} w(t, j) (q_t . k_j) v_j,      n_t . q_t likewise with n_prev and without v,
+//     S_new = exp(b_last + m_prev - m_last) S_prev + sum_j exp(i_j + b_last - b_j - m_last) k_j v_j^T.
+// Every exponent is at most 0.  A fixed decay is the case i = 0, f = log(decay), m = 0.  The piece's rows are asked for together
+// (three round trips to memory a piece instead of three a row); thread (c, g) owns column c of the tile for rows g, g + DS, ..
+constexpr int kPiece = 32;
+
+__global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a, int vt_pow2) {
+    extern __shared__ float smem[];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int seq = blockIdx.x, h = blockIdx.y, nv = blockIdx.z;
+    const int row0 = a.q_start[seq], row1 = a.q_start[seq + 1];
+    if (row1 <= row0) return;
+    const int D = a.D, VT = a.VT, E = a.E, LDQ = D + 1, LDP = kPiece + 1;
+    const int c = threadIdx.x & (vt_pow2 - 1), tg = threadIdx.x / vt_pow2, DS = blockDim.x / vt_pow2;
+    const int col = nv * VT + c;
+    const bool live = c < VT && col < E;
+    const int cc = live ? c : 0;           // threads without a column read column 0 and store nothing
+    float* S = smem;                       // [D][VT]
+    float* ns = S + (size_t)D * VT;        // [D]
+    float* qs = ns + D;                    // [kPiece][LDQ]
+    float* ks = qs + kPiece * LDQ;         // [kPiece][LDQ]
+    float* vs = ks + kPiece * LDQ;         // [kPiece][VT]
+    float* P = vs + kPiece * VT;           // [kPiece][LDP]
+    float* gi = P + kPiece * LDP;          // log input gate of row t
+    float* gb = gi + kPiece;               // b_t
+    float* gm = gb + kPiece;               // m_t
+    float* al = gm + kPiece;               // alpha_t
+    float* uj = al + kPiece;               // row j's factor in the new state
+    float* den = uj + kPiece;              // what divides row t
+    float* sc = den + kPiece;              // [0] the old state's factor in the new one, [1] m_last
+    float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1);
+    const bool gated = a.decay == nullptr;
+    const float logd = gated ? 0.0f : logf(a.decay[h]);       // -inf for a decay of 0: exp gives 0
+    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) S[i] = st[i];
+    float m = st[(size_t)D * VT + D];
+    for (int p0 = row0; p0 < row1; p0 += kPiece) {
+        const int n = min(kPiece, row1 - p0);
+        // The piece's rows: queries and keys rotated and scaled, the tile's values, the gates.
+        for (int idx = threadIdx.x; idx < 2 * n * D; idx += blockDim.x) {
+            const bool is_k = idx >= n * D;
+            const int rem = is_k ? idx - n * D : idx, t = rem / D, d = rem - t * D;
+            const float* src = (is_k ? a.k : a.q) + (size_t)(p0 + t) * a.ld + (size_t)h * D;
+            (is_k ? ks : qs)[t * LDQ + d] = rotated(src, d, a.rot_dims, a.freq, a.positions[p0 + t], is_k ? a.k_scale : a.q_scale);
+        }
+        for (int idx = threadIdx.x; idx < n * VT; idx += blockDim.x) {
+            const int t = idx / VT, x = idx - t * VT;
+            vs[idx] = nv * VT + x < E ? a.v[(size_t)(p0 + t) * a.ld + (size_t)h * E + nv * VT + x] : 0.0f;
+        }
+        if (gated && threadIdx.x < n) {
+            const int row = p0 + threadIdx.x;
+            gi[threadIdx.x] = a.cap * tanhf(a.zi[(size_t)row * a.ld + h] / a.cap);
+            gb[threadIdx.x] = log_sigmoid(a.cap * tanhf(a.zf[(size_t)row * a.ld + h] / a.cap));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && gated) {       // the running maximum and the sums of the forget gates, row after row
+            float mm = m, b = 0.0f;
+            for (int t = 0; t < n; ++t) {
+                const float f = gb[t];
+                mm = fmaxf(f + mm, gi[t]);
+                b += f;
+                gb[t] = b;
+                gm[t] = mm;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < n) {
+            const int t = threadIdx.x;
+            if (gated) {
+                al[t] = expf(gb[t] + m - gm[t]);
+                uj[t] = expf(gi[t] + gb[n - 1] - gb[t] - gm[n - 1]);
+            } else {
+                al[t] = expf((float)(t + 1) * logd);
+                uj[t] = t == n - 1 ? 1.0f : expf((float)(n - 1 - t) * logd);
+            }
+            if (t == 0) {
+                sc[0] = gated ? expf(gb[n - 1] + m - gm[n - 1]) : expf((float)n * logd);
+                sc[1] = gated ? gm[n - 1] : 0.0f;
+            }
+        }
+        // Weighted scores: a warp per row t, lane j.
+        for (int e = threadIdx.x; e < kPiece * kPiece; e += blockDim.x) {
+            const int t = e >> 5, j = e & 31;
+            float p = 0.0f;
+            if (t < n && j <= t) {
+                float dot = 0.0f;
+                for (int d = 0; d < D; ++d) dot = fmaf(qs[t * LDQ + d], ks[j * LDQ + d], dot);
+                const float w = gated ? expf(gi[j] + gb[t] - gb[j] - gm[t]) : (t == j ? 1.0f : expf((float)(t - j) * logd));
+                p = dot * w;
+            }
+            P[t * LDP + j] = p;
+        }
+        __syncthreads();
+        const float m_next = sc[1];
+        if (threadIdx.x < n) {
+            const int t = threadIdx.x;
+            float d = 1.0f;
+            if (gated) {
+                float nq = 0.0f;
+                for (int x = 0; x < D; ++x) nq = fmaf(ns[x], qs[t * LDQ + x], nq);
+                nq *= al[t];
+                for (int j = 0; j <= t; ++j) nq += P[t * LDP + j];
+                d = fmaxf(fabsf(nq), expf(-gm[t])) + 1e-6f;
+            }
+            den[t] = d;
+        }
+        __syncthreads();
+        // Outputs: this thread's rows tg, tg + DS, .. (up to eight) of column c.
+        {
+            float from_state[8], from_piece[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) from_state[r] = from_piece[r] = 0.0f;
+            for (int d = 0; d < D; ++d) {
+                const float s = S[d * VT + cc];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const int t = tg + r * DS;
+                    if (t < kPiece) from_state[r] = fmaf(qs[t * LDQ + d], s, from_state[r]);
+                }
+            }
+            for (int j = 0; j < n; ++j) {
+                const float v = vs[j * VT + cc];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const int t = tg + r * DS;
+                    if (t < kPiece) from_piece[r] = fmaf(P[t * LDP + j], v, from_piece[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int t = tg + r * DS;
+                if (t < n && live) a.out[(size_t)(p0 + t) * a.ldo + (size_t)h * E + col] = (al[t] * from_state[r] + from_piece[r]) / den[t];
+            }
+        }
+        __syncthreads();
+        // The state after the piece.
+        const float keep = sc[0];
+        for (int d0 = tg; d0 < D; d0 += 8 * DS) {
+            float add[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) add[i] = 0.0f;
+            for (int j = 0; j < n; ++j) {
+                const float v = uj[j] * vs[j * VT + cc];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int d = d0 + i * DS;
+                    if (d < D) add[i] = fmaf(ks[j * LDQ + d], v, add[i]);
+                }
+            }
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int d = d0 + i * DS;
+                    if (d < D) S[d * VT + c] = fmaf(keep, S[d * VT + c], add[i]);
+                }
+            }
+        }
+        if (gated)
+            for (int d = threadIdx.x; d < D; d += blockDim.x) {
+                float add = 0.0f;
+                for (int j = 0; j < n; ++j) add = fmaf(uj[j], ks[j * LDQ + d], add);
+                ns[d] = fmaf(keep, ns[d], add);
+            }
+        m = m_next;
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) st[i] = S[i];
+    if (threadIdx.x == 0) st[(size_t)D * VT + D] = m;
+}
+
 }  // namespace
 
 extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
@@ -159,7 +332,14 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
     int p2 = 1;
     while (p2 < value_tile) p2 <<= 1;
     auto s = static_cast<cudaStream_t>(stream);
-    (void)chunked;
+    if (chunked) {
+        const size_t bytes = ((size_t)dim * value_tile + dim + 2 * (size_t)kPiece * (dim + 1) + (size_t)kPiece * value_tile + kPiece * (kPiece + 1) + 6 * kPiece + 2) *
+                             sizeof(float);
+        LB_CHECK_ARG(bytes <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
+        if (bytes > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_chunks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        LB_CHECK_CUDA(lb_launch_overlapped(matrix_memory_chunks_kernel, dim3(n_seq, n_head, a.NV), dim3(256), bytes, s, a, p2));
+        return LB_OK;
+    }
     const size_t smem = ((size_t)dim * value_tile + 3 * (size_t)dim + 256) * sizeof(float);
     LB_CHECK_ARG(smem <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -58,12 +58,20 @@ __global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T
 
 // ---------------------------------------------------------------- plan
 // offsets [E + 1]; place[pair] = where the pair stands in the sorted order; pair_at[place] = the pair.
-__global__ void __launch_bounds__(1024) expert_plan_kernel(const int32_t* __restrict__ ids, int n_pairs, int E, int32_t* __restrict__ offsets,
-                                                           int32_t* __restrict__ place, int32_t* __restrict__ pair_at) {
-    extern __shared__ int counts[];    // [E + 1]
+__global__ void __launch_bounds__(1024) expert_plan_kernel(const int32_t* __restrict__ ids_global, int n_pairs, int E, int32_t* __restrict__ offsets,
+                                                           int32_t* __restrict__ place, int32_t* __restrict__ pair_at, int staged) {
+    extern __shared__ int counts[];    // [E + 1], then the pairs' experts where they fit (`staged`)
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    // Every warp walks all pairs twice: from shared memory where they fit, so that a walk is not a chain of round trips.
+    const int32_t* ids = ids_global;
+    if (staged) {
+        int* mine = counts + E + 1;
+        for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) mine[p] = ids_global[p];
+        ids = mine;
+        __syncthreads();
+    }
     for (int e = warp; e < E; e += n_warps) {
         int n = 0;
         for (int p0 = 0; p0 < n_pairs; p0 += 32) {
@@ -459,8 +467,9 @@ extern "C" int lb_router_topk(int dtype, const void* h, int64_t ldh, const void*
 extern "C" int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at, void* stream) {
     LB_CHECK_ARG(n_pairs >= 0 && n_experts > 0 && n_experts <= 4096, "expert plan: bad sizes");
     const int threads = 32 * max(1, min(32, n_experts));
-    LB_CHECK_CUDA(lb_launch_overlapped(expert_plan_kernel, dim3(1), dim3(threads), (size_t)(n_experts + 1) * sizeof(int), static_cast<cudaStream_t>(stream), ids,
-                                       n_pairs, n_experts, offsets, place, pair_at));
+    const int staged = (size_t)(n_experts + 1 + n_pairs) * sizeof(int) <= 48 * 1024 ? 1 : 0;
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_plan_kernel, dim3(1), dim3(threads), (size_t)(n_experts + 1 + (staged ? n_pairs : 0)) * sizeof(int),
+                                       static_cast<cudaStream_t>(stream), ids, n_pairs, n_experts, offsets, place, pair_at, staged));
     return LB_OK;
 }
 

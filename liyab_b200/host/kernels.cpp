@@ -321,8 +321,9 @@ void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int 
 }
 
 int memory_value_tile(int dim, int vdim) {
-    // Tiles of up to 64 value columns, equal in size; fewer columns where dim x tile floats would not fit a block's shared memory.
-    int cap = 64;
+    // Tiles of up to 32 value columns, equal in size (more tiles, more blocks: a memory's rows of one request and head follow one
+    // another, so the tiles are what fills the GPU); fewer columns where dim x tile floats would not fit a block's shared memory.
+    int cap = 32;
     while (cap > 8 && static_cast<int64_t>(dim) * cap * 4 > 96 * 1024) cap /= 2;
     const int tiles = (vdim + cap - 1) / cap;
     return (vdim + tiles - 1) / tiles;
