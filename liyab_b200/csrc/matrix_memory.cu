@@ -44,6 +44,12 @@ struct MemoryArgs {
     float q_scale, k_scale, cap;
 };
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 
 // Value d of a head's query or key row for the token at `pos`, rotated and scaled.
@@ -139,6 +145,32 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
     if (threadIdx.x == 0) st[(size_t)D * VT + D] = m;
 }
 
+// S[d][c] = keep S[d][c] + sum_j u_j k_j[d] v_j[c] for this thread's column c and its values d = tg, tg + DS, .., N of them at a time.
+template <int N, int DS>
+__device__ __forceinline__ void state_after_piece(float* S, const float* ks, const float* vs, const float* uj, float keep, int tg, int c, int cc, bool live,
+                                                  int n, int D, int VT, int LDQ) {
+    for (int d0 = tg; d0 < D; d0 += N * DS) {
+        float add[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) add[i] = 0.0f;
+        for (int j = 0; j < n; ++j) {
+            const float v = uj[j] * vs[j * VT + cc];
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const int d = d0 + i * DS;
+                if (d < D) add[i] = fmaf(ks[j * LDQ + d], v, add[i]);
+            }
+        }
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const int d = d0 + i * DS;
+                if (d < D) S[d * VT + c] = fmaf(keep, S[d * VT + c], add[i]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- in pieces of 32 rows
 // With b_t the sum of the log forget gates from the piece's start to row t, and m_t the running maximum (by the same recursion
 // as row by row):  w(t, j) = exp(i_j + b_t - b_j - m_t) for j <= t,  alpha_t = exp(b_t + m_prev - m_t),
@@ -148,7 +180,9 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
 // (three round trips to memory a piece instead of three a row); thread (c, g) owns column c of the tile for rows g, g + DS, ..
 constexpr int kPiece = 32;
 
-__global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a, int vt_pow2) {
+template <int VTP, int NT>
+__global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) {
+    constexpr int vt_pow2 = VTP, DS = NT / VTP, R = kPiece / DS, kWarps = NT / 32;      // thread (c, tg) owns column c for the R rows tg, tg + DS, ..
     extern __shared__ float smem[];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -156,7 +190,7 @@ __global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a,
     const int row0 = a.q_start[seq], row1 = a.q_start[seq + 1];
     if (row1 <= row0) return;
     const int D = a.D, VT = a.VT, E = a.E, LDQ = D + 1, LDP = kPiece + 1;
-    const int c = threadIdx.x & (vt_pow2 - 1), tg = threadIdx.x / vt_pow2, DS = blockDim.x / vt_pow2;
+    const int c = threadIdx.x & (vt_pow2 - 1), tg = threadIdx.x / vt_pow2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = nv * VT + c;
     const bool live = c < VT && col < E;
     const int cc = live ? c : 0;           // threads without a column read column 0 and store nothing
@@ -173,6 +207,7 @@ __global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a,
     float* uj = al + kPiece;               // row j's factor in the new state
     float* den = uj + kPiece;              // what divides row t
     float* sc = den + kPiece;              // [0] the old state's factor in the new one, [1] m_last
+    int* pos_s = reinterpret_cast<int*>(sc + 2);      // the rows' positions
     float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1);
     const bool gated = a.decay == nullptr;
     const float logd = gated ? 0.0f : logf(a.decay[h]);       // -inf for a decay of 0: exp gives 0
@@ -180,31 +215,72 @@ __global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a,
     float m = st[(size_t)D * VT + D];
     for (int p0 = row0; p0 < row1; p0 += kPiece) {
         const int n = min(kPiece, row1 - p0);
-        // The piece's rows: queries and keys rotated and scaled, the tile's values, the gates.
-        for (int idx = threadIdx.x; idx < 2 * n * D; idx += blockDim.x) {
-            const bool is_k = idx >= n * D;
-            const int rem = is_k ? idx - n * D : idx, t = rem / D, d = rem - t * D;
-            const float* src = (is_k ? a.k : a.q) + (size_t)(p0 + t) * a.ld + (size_t)h * D;
-            (is_k ? ks : qs)[t * LDQ + d] = rotated(src, d, a.rot_dims, a.freq, a.positions[p0 + t], is_k ? a.k_scale : a.q_scale);
+        // The piece's rows as they are, all asked for at once (4-byte cp.async, one round trip), and the gates.
+        for (int t = warp; t < n; t += kWarps) {          // a warp per row, lanes over the row's values
+            const float* q_row = a.q + (size_t)(p0 + t) * a.ld + (size_t)h * D;
+            const float* k_row = a.k + (size_t)(p0 + t) * a.ld + (size_t)h * D;
+            for (int d = lane; d < D; d += 32) {
+                cp_async4(qs + t * LDQ + d, q_row + d);
+                cp_async4(ks + t * LDQ + d, k_row + d);
+            }
+            const float* v_row = a.v + (size_t)(p0 + t) * a.ld + (size_t)h * E + nv * VT;
+            for (int x = lane; x < VT; x += 32) {
+                if (nv * VT + x < E) cp_async4(vs + t * VT + x, v_row + x);
+                else vs[t * VT + x] = 0.0f;
+            }
         }
-        for (int idx = threadIdx.x; idx < n * VT; idx += blockDim.x) {
-            const int t = idx / VT, x = idx - t * VT;
-            vs[idx] = nv * VT + x < E ? a.v[(size_t)(p0 + t) * a.ld + (size_t)h * E + nv * VT + x] : 0.0f;
-        }
-        if (gated && threadIdx.x < n) {
-            const int row = p0 + threadIdx.x;
-            gi[threadIdx.x] = a.cap * tanhf(a.zi[(size_t)row * a.ld + h] / a.cap);
-            gb[threadIdx.x] = log_sigmoid(a.cap * tanhf(a.zf[(size_t)row * a.ld + h] / a.cap));
-        }
-        __syncthreads();
-        if (threadIdx.x == 0 && gated) {       // the running maximum and the sums of the forget gates, row after row
-            float mm = m, b = 0.0f;
-            for (int t = 0; t < n; ++t) {
-                const float f = gb[t];
-                mm = fmaxf(f + mm, gi[t]);
-                b += f;
+        cp_async_commit();
+        if (threadIdx.x < kPiece) {
+            const int t = threadIdx.x, row = p0 + t;
+            float i_log = -CUDART_INF_F, f_log = 0.0f;
+            if (t < n) {
+                pos_s[t] = a.positions[row];
+                if (gated) {
+                    i_log = a.cap * tanhf(a.zi[(size_t)row * a.ld + h] / a.cap);
+                    f_log = log_sigmoid(a.cap * tanhf(a.zf[(size_t)row * a.ld + h] / a.cap));
+                }
+            }
+            if (gated) {
+                // b_t by a running sum over the lanes; m_t = b_t + max(m_prev, max_{j <= t} (i_j - b_j)), which is the recursion
+                // m_t = max(f_t + m_{t-1}, i_t) written out.
+                float b = f_log;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float up = __shfl_up_sync(0xffffffffu, b, o);
+                    if (t >= o) b += up;
+                }
+                float best = i_log - b;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float up = __shfl_up_sync(0xffffffffu, best, o);
+                    if (t >= o) best = fmaxf(best, up);
+                }
+                gi[t] = i_log;
                 gb[t] = b;
-                gm[t] = mm;
+                gm[t] = b + fmaxf(m, best);
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        // Rotation and scales, in place.
+        {
+            const int half = a.rot_dims >> 1;
+            for (int t = warp; t < n; t += kWarps) {
+                float* q_row = qs + t * LDQ;
+                float* k_row = ks + t * LDQ;
+                for (int d = lane; d < half; d += 32) {
+                    float sn, cs;
+                    sincosf((float)pos_s[t] * a.freq[d], &sn, &cs);
+                    const float ql = q_row[d], qh = q_row[d + half], kl = k_row[d], kh = k_row[d + half];
+                    q_row[d] = (ql * cs - qh * sn) * a.q_scale;
+                    q_row[d + half] = (qh * cs + ql * sn) * a.q_scale;
+                    k_row[d] = (kl * cs - kh * sn) * a.k_scale;
+                    k_row[d + half] = (kh * cs + kl * sn) * a.k_scale;
+                }
+                for (int d = a.rot_dims + lane; d < D; d += 32) {
+                    q_row[d] *= a.q_scale;
+                    k_row[d] *= a.k_scale;
+                }
             }
         }
         __syncthreads();
@@ -223,55 +299,60 @@ __global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a,
             }
         }
         // Weighted scores: a warp per row t, lane j.
-        for (int e = threadIdx.x; e < kPiece * kPiece; e += blockDim.x) {
-            const int t = e >> 5, j = e & 31;
+        for (int t = warp; t < kPiece; t += kWarps) {
+            const int j = lane;
             float p = 0.0f;
+            const float* q_row = qs + t * LDQ;
             if (t < n && j <= t) {
-                float dot = 0.0f;
-                for (int d = 0; d < D; ++d) dot = fmaf(qs[t * LDQ + d], ks[j * LDQ + d], dot);
+                const float* k_row = ks + j * LDQ;
+                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+                int d = 0;
+                for (; d + 3 < D; d += 4) {
+                    d0 = fmaf(q_row[d], k_row[d], d0);
+                    d1 = fmaf(q_row[d + 1], k_row[d + 1], d1);
+                    d2 = fmaf(q_row[d + 2], k_row[d + 2], d2);
+                    d3 = fmaf(q_row[d + 3], k_row[d + 3], d3);
+                }
+                for (; d < D; ++d) d0 = fmaf(q_row[d], k_row[d], d0);
                 const float w = gated ? expf(gi[j] + gb[t] - gb[j] - gm[t]) : (t == j ? 1.0f : expf((float)(t - j) * logd));
-                p = dot * w;
+                p = ((d0 + d1) + (d2 + d3)) * w;
             }
             P[t * LDP + j] = p;
+            // What divides the row: the old n's share (lanes over its values) and the piece's (the row's weighted scores).
+            if (t < n) {
+                float divisor = 1.0f;
+                if (gated) {
+                    float old = 0.0f;
+                    for (int x = lane; x < D; x += 32) old = fmaf(ns[x], q_row[x], old);
+                    const float nq = expf(gb[t] + m - gm[t]) * lb_warp_sum(old) + lb_warp_sum(p);
+                    divisor = fmaxf(fabsf(nq), expf(-gm[t])) + 1e-6f;
+                }
+                if (lane == 0) den[t] = divisor;
+            }
         }
         __syncthreads();
         const float m_next = sc[1];
-        if (threadIdx.x < n) {
-            const int t = threadIdx.x;
-            float d = 1.0f;
-            if (gated) {
-                float nq = 0.0f;
-                for (int x = 0; x < D; ++x) nq = fmaf(ns[x], qs[t * LDQ + x], nq);
-                nq *= al[t];
-                for (int j = 0; j <= t; ++j) nq += P[t * LDP + j];
-                d = fmaxf(fabsf(nq), expf(-gm[t])) + 1e-6f;
-            }
-            den[t] = d;
-        }
-        __syncthreads();
         // Outputs: this thread's rows tg, tg + DS, .. (up to eight) of column c.
         {
-            float from_state[8], from_piece[8];
+            float from_state[R], from_piece[R];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) from_state[r] = from_piece[r] = 0.0f;
+            for (int r = 0; r < R; ++r) from_state[r] = from_piece[r] = 0.0f;
+            const float* q_rows = qs + tg * LDQ;
+            const float* p_rows = P + tg * LDP;
+#pragma unroll 2
             for (int d = 0; d < D; ++d) {
                 const float s = S[d * VT + cc];
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const int t = tg + r * DS;
-                    if (t < kPiece) from_state[r] = fmaf(qs[t * LDQ + d], s, from_state[r]);
-                }
+                for (int r = 0; r < R; ++r) from_state[r] = fmaf(q_rows[r * DS * LDQ + d], s, from_state[r]);
             }
+#pragma unroll 2
             for (int j = 0; j < n; ++j) {
                 const float v = vs[j * VT + cc];
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const int t = tg + r * DS;
-                    if (t < kPiece) from_piece[r] = fmaf(P[t * LDP + j], v, from_piece[r]);
-                }
+                for (int r = 0; r < R; ++r) from_piece[r] = fmaf(p_rows[r * DS * LDP + j], v, from_piece[r]);
             }
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
+            for (int r = 0; r < R; ++r) {
                 const int t = tg + r * DS;
                 if (t < n && live) a.out[(size_t)(p0 + t) * a.ldo + (size_t)h * E + col] = (al[t] * from_state[r] + from_piece[r]) / den[t];
             }
@@ -279,26 +360,9 @@ __global__ void __launch_bounds__(256) matrix_memory_chunks_kernel(MemoryArgs a,
         __syncthreads();
         // The state after the piece.
         const float keep = sc[0];
-        for (int d0 = tg; d0 < D; d0 += 8 * DS) {
-            float add[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) add[i] = 0.0f;
-            for (int j = 0; j < n; ++j) {
-                const float v = uj[j] * vs[j * VT + cc];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int d = d0 + i * DS;
-                    if (d < D) add[i] = fmaf(ks[j * LDQ + d], v, add[i]);
-                }
-            }
-            if (live) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int d = d0 + i * DS;
-                    if (d < D) S[d * VT + c] = fmaf(keep, S[d * VT + c], add[i]);
-                }
-            }
-        }
+        if (D <= 2 * DS) state_after_piece<2, DS>(S, ks, vs, uj, keep, tg, c, cc, live, n, D, VT, LDQ);
+        else if (D <= 4 * DS) state_after_piece<4, DS>(S, ks, vs, uj, keep, tg, c, cc, live, n, D, VT, LDQ);
+        else state_after_piece<8, DS>(S, ks, vs, uj, keep, tg, c, cc, live, n, D, VT, LDQ);
         if (gated)
             for (int d = threadIdx.x; d < D; d += blockDim.x) {
                 float add = 0.0f;
@@ -333,12 +397,18 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
     while (p2 < value_tile) p2 <<= 1;
     auto s = static_cast<cudaStream_t>(stream);
     if (chunked) {
-        const size_t bytes = ((size_t)dim * value_tile + dim + 2 * (size_t)kPiece * (dim + 1) + (size_t)kPiece * value_tile + kPiece * (kPiece + 1) + 6 * kPiece + 2) *
+        const size_t bytes = ((size_t)dim * value_tile + dim + 2 * (size_t)kPiece * (dim + 1) + (size_t)kPiece * value_tile + kPiece * (kPiece + 1) + 7 * kPiece + 2) *
                              sizeof(float);
         LB_CHECK_ARG(bytes <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
-        if (bytes > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_chunks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-        LB_CHECK_CUDA(lb_launch_overlapped(matrix_memory_chunks_kernel, dim3(n_seq, n_head, a.NV), dim3(256), bytes, s, a, p2));
-        return LB_OK;
+        auto launch = [&](auto kernel, int threads) -> int {
+            if (bytes > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+            LB_CHECK_CUDA(lb_launch_overlapped(kernel, dim3(n_seq, n_head, a.NV), dim3(threads), bytes, s, a));
+            return LB_OK;
+        };
+        if (p2 <= 8) return launch(matrix_memory_chunks_kernel<8, 256>, 256);
+        if (p2 == 16) return launch(matrix_memory_chunks_kernel<16, 512>, 512);
+        if (p2 == 32) return launch(matrix_memory_chunks_kernel<32, 512>, 512);
+        return launch(matrix_memory_chunks_kernel<64, 512>, 512);
     }
     const size_t smem = ((size_t)dim * value_tile + 3 * (size_t)dim + 256) * sizeof(float);
     LB_CHECK_ARG(smem <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);

@@ -53,9 +53,9 @@ def make_engine(path, dtype, max_tokens, **options):
 def check(got, want, dtype, rel_tol=REL_TOL, flips=True):
     """float32: every logit within rel_tol of the plain model's.  bfloat16: per row, the root mean square of the
     difference (its mean taken off) over that of the sequence's logits; 8 bits of mantissa put it near a percent, and the
-    mean is held to 2 %.  Where two experts' scores lie close, a rounding sends a row to another expert, and the memories
+    median is held to 1.5 %, the mean to 2 %.  Where two experts' scores lie close, a rounding sends a row to another expert, and the memories
     carry that difference to the positions after it (`flips`): then up to a tenth of the rows may lie beyond 6 %, none beyond
-    the logits' own spread.  Models whose routers decide by clear margins are held to 6 % in every row."""
+    the logits' own spread, and the mean is held to 4 %.  Models whose routers decide by clear margins are held to 6 % in every row."""
     if dtype != "bfloat16":
         return tt.check_rows(got, want, rel_tol)
     errs = []
@@ -64,11 +64,12 @@ def check(got, want, dtype, rel_tol=REL_TOL, flips=True):
         spread = want[r] - want[r].mean(axis=-1, keepdims=True)
         errs.append(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((spread ** 2).mean()))
     errs = np.asarray(errs)
-    assert np.isfinite(errs).all() and errs.mean() <= 2e-2, f"mean relative error {errs.mean():.3e}"
+    assert np.isfinite(errs).all() and np.median(errs) <= 1.5e-2, f"median relative error {np.median(errs):.3e}"
     if flips:
+        assert errs.mean() <= 4e-2, f"mean relative error {errs.mean():.3e}"
         assert (errs > 6e-2).mean() <= 0.10 and errs.max() < 1.0, f"{(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %, the worst by {errs.max():.2f}"
     else:
-        assert errs.max() <= 6e-2, f"{(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %"
+        assert errs.mean() <= 2e-2 and errs.max() <= 6e-2, f"mean {errs.mean():.3e}, {(errs > 6e-2).sum()} of {len(errs)} rows are off by more than 6 %"
     return {"mean": float(errs.mean()), "worst": float(errs.max())}
 
 
