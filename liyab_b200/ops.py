@@ -595,3 +595,124 @@ def latent_attention(wide: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Ten
                                         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out", torch.float32),
                                         out.stride(0), T, n_head, rank, rot, page_size, float(scale), window, stream_ptr()), "latent_attention")
     return out
+
+
+# ---- gated mixers, matrix memories, routed experts -----------------------------------------------------------------
+for _name, _args in {
+    "lb_rms_groups_offset": [_i, _p, _l, _p, _p, _f, _p, _l, _i, _i, _i, _f, _p],
+    "lb_add_row": [_p, _l, _p, _i, _i, _p],
+    "lb_rms_sum_add": [_p, _l, _i, _p, _p, _p, _i, _i, _f, _f, _p],
+    "lb_qk_norm_store": [_i, _p, _l, _i, _i, _i, _p, _p, _p, _l, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    "lb_head_gate": [_i, _i, _p, _l, _i, _p, _l, _p, _p, _l, _i, _i, _i, _i, _i, _f, _p],
+    "lb_gated_act": [_i, _p, _l, _p, _l, _i, _i, _i, _p],
+    "lb_matrix_memory": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _p],
+    "lb_router_topk": [_i, _p, _l, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "lb_expert_plan": [_p, _i, _i, _p, _p, _p, _p],
+    "lb_expert_product": [_i, _i, _p, _l, _p, _l, _p, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
+    "lb_expert_product_set_plain": [_i],
+    "lb_expert_combine": [_p, _l, _p, _l, _p, _i, _i, _i, _p],
+}.items():
+    _SIGNATURES[_name] = _args
+
+GATES = {"sigmoid": 0, "silu": 1, "gelu_tanh": 2}
+
+
+def rms_offset(x: torch.Tensor, weight: torch.Tensor, gain_offset: float, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * (gain_offset + weight)."""
+    check(lib().lb_rms_groups_offset(_code(out.dtype, "out"), _dev(x, "x", torch.float32), x.stride(0), None, _dev(weight, "weight", torch.float32),
+                                     float(gain_offset), _dev(out, "out"), out.stride(0), out.shape[0], x.shape[1], 1, float(eps), stream_ptr()), "rms_groups_offset")
+    return out
+
+
+def add_row(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    check(lib().lb_add_row(_dev(x, "x", torch.float32), x.stride(0), _dev(v, "v", torch.float32), x.shape[0], x.shape[1], stream_ptr()), "add_row")
+    return x
+
+
+def rms_sum_add(x: torch.Tensor, branches, weights, scale: float, eps: float) -> torch.Tensor:
+    """x[r] += scale * sum_i rms(branches[i][r]) * weights[i] (float32 rows; a weight may be None)."""
+    n = len(branches)
+    ys = (_c.c_void_p * n)(*[_dev(y, "branch", torch.float32) for y in branches])
+    ld = (_c.c_int64 * n)(*[y.stride(0) for y in branches])
+    ws = (_c.c_void_p * n)(*[_opt(w, "weight", torch.float32) for w in weights])
+    check(lib().lb_rms_sum_add(_dev(x, "x", torch.float32), x.stride(0), n, ys, ld, ws, x.shape[0], x.shape[1], float(scale), float(eps), stream_ptr()), "rms_sum_add")
+    return x
+
+
+def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                  q_out: torch.Tensor, cache: Optional[torch.Tensor], slot_mapping: torch.Tensor, n_head: int, n_kv_head: int, dim: int, vdim: int,
+                  padded: int, page_size: int, norm: bool, eps: float) -> torch.Tensor:
+    """Queries, keys and values of the float rows `proj` (see csrc/api.h): normalised per head, padded to `padded` values, keys and values
+    into the cache pages [page, K|V, kv_head, slot, padded]."""
+    check(lib().lb_qk_norm_store(_code(q_out.dtype, "q_out"), _dev(proj, "proj", torch.float32), proj.stride(0), q_off, k_off, v_off,
+                                 _opt(q_weight, "q_weight", torch.float32), _opt(k_weight, "k_weight", torch.float32), _dev(q_out, "q_out"), q_out.stride(0),
+                                 _opt(cache, "cache", q_out.dtype), _dev(slot_mapping, "slot_mapping", torch.int32), proj.shape[0], n_head, n_kv_head, dim, vdim,
+                                 padded, page_size, int(norm), float(eps), stream_ptr()), "qk_norm_store")
+    return q_out
+
+
+def head_gate(o: torch.Tensor, o_head: int, g: Optional[torch.Tensor], gain: Optional[torch.Tensor], out: torch.Tensor, n_head: int, vdim: int, norm: bool,
+              gate: str, eps: float) -> torch.Tensor:
+    """out[t, h, :] = (o[t, h, :vdim] over its root mean square when `norm`) * gain * gate(g[t, h, :])."""
+    check(lib().lb_head_gate(_code(o.dtype, "o"), _code(out.dtype, "out"), _dev(o, "o"), o.stride(0), o_head, _opt(g, "g", torch.float32),
+                             g.stride(0) if g is not None else 0, _opt(gain, "gain", torch.float32), _dev(out, "out"), out.stride(0), o.shape[0], n_head, vdim,
+                             int(norm), GATES[gate], float(eps), stream_ptr()), "head_gate")
+    return out
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, gate: str) -> torch.Tensor:
+    check(lib().lb_gated_act(_code(out.dtype, "out"), _dev(gu, "gu", torch.float32), gu.stride(0), _dev(out, "out"), out.stride(0), gu.shape[0], out.shape[1],
+                             GATES[gate], stream_ptr()), "gated_act")
+    return out
+
+
+def memory_slot_floats(n_head: int, dim: int, vdim: int, value_tile: int) -> int:
+    return n_head * ((vdim + value_tile - 1) // value_tile) * (dim * value_tile + dim + 1)
+
+
+def matrix_memory(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
+                  freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+                  out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float, chunked: bool) -> torch.Tensor:
+    """The matrix memories of csrc/matrix_memory.cu over the float rows `proj` whose columns hold q, k, v (and the gates' pre-activations) at the
+    given offsets; state [slots, memory_slot_floats(..)] float32."""
+    base = _dev(proj, "proj", torch.float32)
+    at = lambda off: None if off is None else base + 4 * off
+    check(lib().lb_matrix_memory(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+                                 _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32), _dev(q_start, "q_start", torch.int32),
+                                 _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32), state.stride(0), _dev(out, "out", torch.float32),
+                                 out.stride(0), q_start.numel() - 1, n_head, dim, vdim, value_tile, float(q_scale), float(k_scale), float(cap), int(chunked),
+                                 stream_ptr()), "matrix_memory")
+    return out
+
+
+def routed_experts(h: torch.Tensor, router: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, x: torch.Tensor, top: int, gate: str = "silu",
+                   softmax: bool = False, renormalise: bool = False, plain: bool = False):
+    """x[t] += sum over row t's `top` experts e of down_e (gate(W_gate_e a) * (W_up_e a)), a = score * h[t]: the router, the plan, the experts' two
+    products and the sum, as the feed-forward part launches them.  gate_up [E, 2 inner, width], down [E, width, inner].  `plain`: bfloat16 products
+    on the 32-bit units.  Returns (ids, weights) [T, top]."""
+    T, width = h.shape
+    E, inner = gate_up.shape[0], gate_up.shape[1] // 2
+    dev = h.device
+    ids = torch.empty(T, top, dtype=torch.int32, device=dev)
+    weights = torch.empty(T, top, dtype=torch.float32, device=dev)
+    place = torch.empty(T * top, dtype=torch.int32, device=dev)
+    pair_at = torch.empty(T * top, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    mid = torch.empty(T * top, inner, dtype=h.dtype, device=dev)
+    y = torch.empty(T * top, width, dtype=torch.float32, device=dev)
+    s = stream_ptr()
+    check(lib().lb_router_topk(_code(h.dtype, "h"), _dev(h, "h"), h.stride(0), _dev(router, "router", h.dtype), _dev(ids, "ids"), _dev(weights, "weights"), T, E,
+                               width, top, int(softmax), int(renormalise), s), "router_topk")
+    check(lib().lb_expert_plan(_dev(ids, "ids"), T * top, E, _dev(offsets, "offsets"), _dev(place, "place"), _dev(pair_at, "pair_at"), s), "expert_plan")
+    lib().lb_expert_product_set_plain(int(plain))
+    try:
+        check(lib().lb_expert_product(_code(h.dtype, "h"), 1, _dev(h, "h"), h.stride(0), _dev(gate_up, "gate_up", h.dtype), 2 * inner * width, _dev(offsets, "offsets"),
+                                      _dev(pair_at, "pair_at"), _dev(weights, "weights"), _dev(mid, "mid"), mid.stride(0), T * top, E, inner, width, top, GATES[gate], s),
+              "expert_product")
+        check(lib().lb_expert_product(_code(h.dtype, "h"), 0, _dev(mid, "mid"), mid.stride(0), _dev(down, "down", h.dtype), width * inner, _dev(offsets, "offsets"),
+                                      _dev(pair_at, "pair_at"), _dev(weights, "weights"), _dev(y, "y"), y.stride(0), T * top, E, width, inner, top, GATES[gate], s),
+              "expert_product")
+    finally:
+        lib().lb_expert_product_set_plain(0)
+    check(lib().lb_expert_combine(_dev(x, "x", torch.float32), x.stride(0), _dev(y, "y"), y.stride(0), _dev(place, "place"), T, width, top, s), "expert_combine")
+    return ids, weights
