@@ -27,10 +27,22 @@ __global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T
     lb_dependents_may_launch();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const T* row = h + (size_t)t * ldh;
+    // A warp per expert; a lane's terms are asked for eight at a time, so that a short row is one or two round trips.  The order of
+    // a lane's sum stays ascending, so z does not depend on the batch.
     for (int e = warp; e < E; e += n_warps) {
         const T* w = router + (size_t)e * width;
         float acc = 0.0f;
-        for (int c = lane; c < width; c += 32) acc = fmaf(lb_to_float(row[c]), lb_to_float(w[c]), acc);
+        for (int c0 = lane; c0 < width; c0 += 32 * 8) {
+            float a[8], b[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int c = c0 + 32 * u;
+                a[u] = c < width ? lb_to_float(row[c]) : 0.0f;
+                b[u] = c < width ? lb_to_float(w[c]) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = fmaf(a[u], b[u], acc);
+        }
         acc = lb_warp_sum(acc);
         if (lane == 0) z[e] = acc;
     }
@@ -454,11 +466,12 @@ extern "C" int lb_router_topk(int dtype, const void* h, int64_t ldh, const void*
     if (n_rows == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)n_experts * sizeof(float);
+    const int threads = 32 * max(1, min(16, n_experts));       // a warp per expert, up to sixteen
     if (dtype == LB_F32)
-        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<float>, dim3(n_rows), dim3(128), smem, s, (const float*)h, ldh, (const float*)router, ids, weights,
+        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)h, ldh, (const float*)router, ids, weights,
                                            n_experts, width, top, softmax, renormalise));
     else if (dtype == LB_BF16)
-        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), smem, s, (const __nv_bfloat16*)h, ldh,
+        LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, (const __nv_bfloat16*)h, ldh,
                                            (const __nv_bfloat16*)router, ids, weights, n_experts, width, top, softmax, renormalise));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "router: unknown dtype %d", dtype);
     return LB_OK;
