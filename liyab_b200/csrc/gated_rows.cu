@@ -37,12 +37,47 @@ __global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches 
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int r = blockIdx.x;
+    // Rows of up to four values a thread are read once, all branches' values asked for together, and kept in registers.
+    constexpr int kKeep = 4;
+    const bool kept = width <= kKeep * (int)blockDim.x;
+    float held[4][kKeep];
+    if (kept) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < kKeep; ++e) {
+                const int c = threadIdx.x + e * blockDim.x;
+                held[i][e] = (i < b.n && c < width) ? b.y[i][(size_t)r * b.ld[i] + c] : 0.0f;
+            }
+    }
     float inv[4];
     for (int i = 0; i < b.n; ++i) {
         const float* y = b.y[i] + (size_t)r * b.ld[i];
         float ss = 0.0f;
-        for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(y[c], y[c], ss);
+        if (kept) {
+#pragma unroll
+            for (int e = 0; e < kKeep; ++e) ss = fmaf(held[i][e], held[i][e], ss);
+        } else {
+            for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(y[c], y[c], ss);
+        }
         inv[i] = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    }
+    if (kept) {
+#pragma unroll
+        for (int e = 0; e < kKeep; ++e) {
+            const int c = threadIdx.x + e * blockDim.x;
+            if (c >= width) break;
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (i >= b.n) break;
+                float v = held[i][e] * inv[i];
+                if (b.w[i] != nullptr) v *= b.w[i][c];
+                acc += v;
+            }
+            x[(size_t)r * ldx + c] += scale * acc;
+        }
+        return;
     }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float acc = 0.0f;
@@ -178,7 +213,7 @@ extern "C" int lb_rms_sum_add(float* x, int64_t ldx, int n_branches, const float
         b.ld[i] = ldy[i];
         b.w[i] = weight != nullptr ? weight[i] : nullptr;
     }
-    const int threads = width >= 1024 ? 256 : 128;
+    const int threads = width > 512 ? 256 : 128;
     LB_CHECK_CUDA(lb_launch_overlapped(rms_sum_add_kernel, dim3(n_rows), dim3(threads), 0, static_cast<cudaStream_t>(stream), x, ldx, b, width, scale, eps));
     return LB_OK;
 }

@@ -250,9 +250,9 @@ __global__ void __launch_bounds__(256) expert_product_kernel(ProductArgs p) {
 }
 
 // ---------------------------------------------------------------- the same products on the tensor cores (bfloat16)
-// 64 rows x 64 features a block, K in steps of 32, four warps of 16 rows each (`mma.sync m16n8k16`, 32-bit sums).  The weights'
-// tiles come by cp.async, the rows' through registers (the first half multiplies them by the pair's weight in 32-bit and rounds
-// once); two stages, so the next step's operands travel under this step's products.  Needs K, the rows' stride and the
+// 64 rows x 64 features a block, K in steps of 32, four warps of 16 rows each (`mma.sync m16n8k16`, 32-bit sums).  Both operands'
+// tiles come by cp.async through a ring of three stages, two steps ahead of the products; the first half multiplies its 32-bit sums
+// by the pair's weight before the gate (the weight on the expert's input, moved past the two linear maps).  Needs K, the rows' stride and the
 // experts' stride to be multiples of 8 elements and 16-byte aligned bases.
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -260,7 +260,6 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -271,13 +270,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kMM = 64, kMN = 64, kMK = 32, kMLD = kMK + 8;
+constexpr int kMM = 64, kMN = 64, kMK = 32, kMLD = kMK + 8, kMStages = 3;
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <bool GATED>
 __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) {
     using B16 = __nv_bfloat16;
-    __shared__ __align__(16) B16 As[2][kMM][kMLD];
-    __shared__ __align__(16) B16 Bs[2][GATED ? 2 : 1][kMN][kMLD];
+    __shared__ __align__(16) B16 As[kMStages][kMM][kMLD];
+    __shared__ __align__(16) B16 Bs[kMStages][GATED ? 2 : 1][kMN][kMLD];
     __shared__ int tile_info[2];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -304,9 +305,9 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
     const B16* W = static_cast<const B16*>(p.w) + (size_t)e * p.expert_stride;
     const B16* A = static_cast<const B16*>(p.a);
 
-    // This thread's two 16-byte pieces of every A tile and of every B tile: piece v -> (row v / 4, elements (v % 4) * 8 ..).
+    // This thread's two 16-byte pieces of every A tile and of every B tile: piece v -> (row v / 4, elements (v % 4) * 8 ..).  The first
+    // half's rows are the pairs' rows of h as they are: the pair's weight multiplies the sums in the epilogue (W (w h) = w (W h)).
     const B16* a_src[2];
-    float a_scale[2];
     const B16* b_src[2];
     int piece_row[2], piece_k[2];
 #pragma unroll
@@ -316,51 +317,19 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
         piece_k[i] = (v & 3) * 8;
         const int r = r0 + piece_row[i];
         a_src[i] = nullptr;
-        a_scale[i] = 1.0f;
-        if (r < r_end) {
-            if (GATED) {
-                const int pair = p.pair_at[r];
-                a_src[i] = A + (size_t)(pair / p.top) * p.lda;
-                a_scale[i] = p.weights[pair];
-            } else {
-                a_src[i] = A + (size_t)r * p.lda;
-            }
-        }
+        if (r < r_end) a_src[i] = GATED ? A + (size_t)(p.pair_at[r] / p.top) * p.lda : A + (size_t)r * p.lda;
         const int n = n0 + piece_row[i];
         b_src[i] = n < p.N ? W + (size_t)n * p.K : nullptr;
     }
-    uint4 a_regs[2];
-    auto fetch_a = [&](int k0) {
+    auto fetch = [&](int k0, int stage) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int k = k0 + piece_k[i];
-            a_regs[i] = (a_src[i] != nullptr && k < p.K) ? *reinterpret_cast<const uint4*>(a_src[i] + k) : make_uint4(0u, 0u, 0u, 0u);
+            const bool a_ok = a_src[i] != nullptr && k < p.K, b_ok = b_src[i] != nullptr && k < p.K;
+            cp_async16(&As[stage][piece_row[i]][piece_k[i]], a_ok ? a_src[i] + k : W, a_ok);
+            cp_async16(&Bs[stage][0][piece_row[i]][piece_k[i]], b_ok ? b_src[i] + k : W, b_ok);
+            if (GATED) cp_async16(&Bs[stage][1][piece_row[i]][piece_k[i]], b_ok ? b_src[i] + (size_t)p.N * p.K + k : W, b_ok);
         }
-    };
-    auto store_a = [&](int stage) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint4 v = a_regs[i];
-            if (GATED) {
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __bfloat1622float2(h2[j]);
-                    h2[j] = __floats2bfloat162_rn(f.x * a_scale[i], f.y * a_scale[i]);
-                }
-            }
-            *reinterpret_cast<uint4*>(&As[stage][piece_row[i]][piece_k[i]]) = v;
-        }
-    };
-    auto fetch_b = [&](int k0, int stage) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int k = k0 + piece_k[i];
-            const bool ok = b_src[i] != nullptr && k < p.K;
-            cp_async16(&Bs[stage][0][piece_row[i]][piece_k[i]], ok ? b_src[i] + k : W, ok);
-            if (GATED) cp_async16(&Bs[stage][1][piece_row[i]][piece_k[i]], ok ? b_src[i] + (size_t)p.N * p.K + k : W, ok);
-        }
-        cp_async_commit();
     };
 
     float acc[8][4], acc2[GATED ? 8 : 1][4];
@@ -372,18 +341,18 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
             if (GATED) acc2[i][j] = 0.0f;
         }
     const int steps = (p.K + kMK - 1) / kMK;
-    fetch_a(0);
-    fetch_b(0, 0);
-    store_a(0);
+    // kMStages - 1 steps ahead; one group per step, empty past the last.
+#pragma unroll
+    for (int i = 0; i < kMStages - 1; ++i) {
+        if (i < steps) fetch(i * kMK, i);
+        cp_async_commit();
+    }
     for (int it = 0; it < steps; ++it) {
-        const int stage = it & 1;
-        cp_async_wait_all();
-        __syncthreads();
-        const bool more = it + 1 < steps;
-        if (more) {
-            fetch_b((it + 1) * kMK, stage ^ 1);
-            fetch_a((it + 1) * kMK);
-        }
+        const int stage = it % kMStages;
+        cp_async_wait<kMStages - 2>();          // this step's group
+        __syncthreads();                        // .. from every thread; and everyone is done with the stage that is filled next
+        if (it + kMStages - 1 < steps) fetch((it + kMStages - 1) * kMK, (it + kMStages - 1) % kMStages);
+        cp_async_commit();
         const int mat = lane >> 3, r = lane & 7;
 #pragma unroll
         for (int kk = 0; kk < kMK / 16; ++kk) {
@@ -402,7 +371,13 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
                 }
             }
         }
-        if (more) store_a(stage ^ 1);
+    }
+    // The rows' weights (first half), then the gate.
+    float w_lo = 1.0f, w_hi = 1.0f;
+    if (GATED) {
+        const int lo = r0 + warp * 16 + g, hi = lo + 8;
+        if (lo < r_end) w_lo = p.weights[p.pair_at[lo]];
+        if (hi < r_end) w_hi = p.weights[p.pair_at[hi]];
     }
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt)
@@ -411,9 +386,10 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
             const int row = r0 + warp * 16 + g + (e4 >= 2 ? 8 : 0), n = n0 + nt * 8 + 2 * t + (e4 & 1);
             if (row >= r_end || n >= p.N) continue;
             if (GATED) {
-                const float z = acc[nt][e4];
+                const float w = e4 >= 2 ? w_hi : w_lo;
+                const float z = w * acc[nt][e4];
                 const float a = p.act == 1 ? z * lb_sigmoid(z) : p.act == 2 ? lb_gelu_tanh(z) : lb_sigmoid(z);
-                static_cast<B16*>(p.out)[(size_t)row * p.ldo + n] = __float2bfloat16_rn(a * acc2[nt][e4]);
+                static_cast<B16*>(p.out)[(size_t)row * p.ldo + n] = __float2bfloat16_rn(a * (w * acc2[nt][e4]));
             } else {
                 static_cast<float*>(p.out)[(size_t)row * p.ldo + n] = acc[nt][e4];
             }
