@@ -298,8 +298,8 @@ def vosurax_config(size, layers=0):
     blocks = []
     for i in range(L):
         if i % 4 == 0:
-            decay = [1.0 - 2.0 ** (-5 - 4 * h / H) for h in range(H)]
-            blocks.append(dict(type="retention", mixer=dict(heads=H, dim=64, vdim=128, decay=decay, rot=dict(base=1e6, dims=32)), mlp=dict(kind="dense", ff=g["n_inner"])))
+            decay = [1.0 - 2.0 ** (-4 - 5 * h / H) for h in range(H)]
+            blocks.append(dict(type="retention", mixer=dict(heads=H, dim=64, vdim=128, decay=decay, rot=dict(base=1e5, dims=32)), mlp=dict(kind="dense", ff=g["n_inner"])))
         else:
             mixer = dict(left=dict(heads=H, kv_heads=max(1, H // 4), dim=64, vdim=64, scale=0.125, mask=dict(size=512)),
                          right=dict(heads=max(1, H // 2), dim=64, vdim=128, gate_cap=15.0))

@@ -82,7 +82,9 @@ __device__ __forceinline__ void gates(const MemoryArgs& a, int row, int h, float
 }
 
 // ---------------------------------------------------------------- row by row
-// 256 threads: thread (c, ds) owns rows ds, ds + DS, .. of column c of the tile's S (in shared memory).
+// 256 threads: thread (c, ds) owns rows ds, ds + DS, .. of column c of the tile's S (in shared memory).  The state and the first
+// row's queries, keys and values are asked for together (4-byte cp.async), and every further row a row ahead, so that a decode
+// step is one round trip to memory and a short portion one per row.
 __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, int vt_pow2) {
     extern __shared__ float smem[];
     lb_wait_for_predecessor();
@@ -96,29 +98,51 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
     const bool live = c < VT && col < E;
     float* S = smem;                       // [D][VT]
     float* ns = S + (size_t)D * VT;        // [D]
-    float* qs = ns + D;                    // [D]
+    float* qs = ns + D;                    // [D] rotated and scaled
     float* ks = qs + D;                    // [D]
     float* red = ks + D;                   // [DS][vt_pow2]
+    float* raw = red + 256;                // [2][2 D + VT]: a row's queries, keys and values as they arrive, two rows in turn
+    const int raw_row = 2 * D + VT;
     float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1);
     const bool gated = a.decay == nullptr;
-    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) S[i] = st[i];       // S and n lie one after the other
+    auto ask = [&](int row, int buffer) {
+        float* dst = raw + buffer * raw_row;
+        const float* q_row = a.q + (size_t)row * a.ld + (size_t)h * D;
+        const float* k_row = a.k + (size_t)row * a.ld + (size_t)h * D;
+        const float* v_row = a.v + (size_t)row * a.ld + (size_t)h * E + nv * VT;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            cp_async4(dst + d, q_row + d);
+            cp_async4(dst + D + d, k_row + d);
+        }
+        for (int x = threadIdx.x; x < VT; x += blockDim.x) {
+            if (nv * VT + x < E) cp_async4(dst + 2 * D + x, v_row + x);
+            else dst[2 * D + x] = 0.0f;
+        }
+    };
+    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) cp_async4(S + i, st + i);       // S and n lie one after the other
+    ask(row0, 0);
+    cp_async_commit();
     float m = st[(size_t)D * VT + D];
-    __syncthreads();
     for (int row = row0; row < row1; ++row) {
+        const int buffer = (row - row0) & 1;
         const int pos = a.positions[row];
         float keep, take, m_new;
         gates(a, row, h, m, &keep, &take, &m_new);
         m = m_new;
+        cp_async_wait_all();
+        __syncthreads();                   // the row has arrived; everyone is done with the row before
+        if (row + 1 < row1) ask(row + 1, buffer ^ 1);
+        cp_async_commit();
+        const float* mine = raw + buffer * raw_row;
         for (int d = threadIdx.x; d < 2 * D; d += blockDim.x) {
             const bool is_k = d >= D;
             const int dd = is_k ? d - D : d;
-            const float* src = (is_k ? a.k : a.q) + (size_t)row * a.ld + (size_t)h * D;
-            (is_k ? ks : qs)[dd] = rotated(src, dd, a.rot_dims, a.freq, pos, is_k ? a.k_scale : a.q_scale);
+            (is_k ? ks : qs)[dd] = rotated(mine + (is_k ? D : 0), dd, a.rot_dims, a.freq, pos, is_k ? a.k_scale : a.q_scale);
         }
         __syncthreads();
         float acc = 0.0f;
         if (live) {
-            const float tv = take * a.v[(size_t)row * a.ld + (size_t)h * E + col];
+            const float tv = take * mine[2 * D + c];
             for (int d = ds; d < D; d += DS) {
                 const float s = fmaf(keep, S[d * VT + c], ks[d] * tv);
                 S[d * VT + c] = s;
@@ -139,8 +163,9 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
             }
             a.out[(size_t)row * a.ldo + (size_t)h * E + col] = o;
         }
-        __syncthreads();
     }
+    cp_async_wait_all();
+    __syncthreads();
     for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) st[i] = S[i];
     if (threadIdx.x == 0) st[(size_t)D * VT + D] = m;
 }
@@ -410,7 +435,7 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
         if (p2 == 32) return launch(matrix_memory_chunks_kernel<32, 512>, 512);
         return launch(matrix_memory_chunks_kernel<64, 512>, 512);
     }
-    const size_t smem = ((size_t)dim * value_tile + 3 * (size_t)dim + 256) * sizeof(float);
+    const size_t smem = ((size_t)dim * value_tile + 3 * (size_t)dim + 256 + 2 * (2 * (size_t)dim + value_tile)) * sizeof(float);
     LB_CHECK_ARG(smem <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LB_CHECK_CUDA(lb_launch_overlapped(matrix_memory_rows_kernel, dim3(n_seq, n_head, a.NV), dim3(256), smem, s, a, p2));

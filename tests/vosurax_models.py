@@ -48,20 +48,20 @@ CONFIG_A = dict(architecture="Vosurax", vocab=160, width=96, norm=dict(eps=1e-5)
     layer(retention(1, 32, 16, [0.98], 32), moe(4, 1, 16)),
 ])
 CONFIG_B = dict(architecture="Vosurax", vocab=200, width=128, norm=dict(eps=1e-6), loop=dict(start=0, stop=2, times=2), layers=[
-    layer(side_by_side(4, 1, 64, 64, 0.125, 64, 2, 32, 64, 12.0), moe(8, 2, 64, 64)),
-    layer(retention(2, 32, 64, [0.96, 0.999], 16, 1e6), dense(256)),
+    layer(side_by_side(4, 2, 64, 64, 0.125, 32, 2, 32, 64, 9.0), moe(8, 2, 64, 64)),
+    layer(retention(2, 32, 64, [0.95, 0.9975], 16, 5e5), dense(256)),
     layer(side_by_side(8, 2, 32, 32, 0.18, 48, 4, 16, 32, 8.0), dense(128)),
 ])
 CONFIG_C = dict(architecture="Vosurax", vocab=97, width=100, norm=dict(eps=1e-4), loop=dict(start=2, stop=3, times=1), layers=[
     layer(side_by_side(6, 1, 24, 40, 0.2, 1, 3, 10, 70, 6.0), moe(3, 3, 20, 12)),
     layer(side_by_side(2, 2, 10, 6, 0.4, 1000, 1, 20, 130, 20.0), dense(50)),
-    layer(side_by_side(5, 5, 8, 8, 0.35, 0, 2, 6, 10, 12.0), None),
+    layer(side_by_side(5, 5, 8, 8, 0.35, 0, 2, 6, 10, 13.0), None),
     layer(retention(2, 10, 70, [0.5, 1.0], 6, 77.0), moe(5, 2, 8, 0)),
 ])
 CONFIG_D = dict(architecture="Vosurax", vocab=64, width=48, norm=dict(eps=1e-5), layers=[
     layer(retention(1, 2, 1, [0.9], 2, 10.0), moe(1, 1, 8, 8)),
     layer(side_by_side(1, 1, 1, 1, 1.0, 16, 1, 1, 1, 1.0), dense(1)),
-    layer(side_by_side(2, 1, 16, 16, 0.25, 31, 1, 16, 16, 12.0), dense(48)),
+    layer(side_by_side(2, 1, 16, 16, 0.25, 31, 1, 16, 16, 11.0), dense(48)),
 ])
 CONFIGS = {"A": (CONFIG_A, 21), "B": (CONFIG_B, 22), "C": (CONFIG_C, 23), "D": (CONFIG_D, 24)}
 
