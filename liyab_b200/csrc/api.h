@@ -282,6 +282,11 @@ int lb_decode_stack_status_set(int value);
 int lb_gemm_tcgen05_withhold_next(int on);
 int lb_decode_stack_withhold_next(int on);
 
+/* lb_gemm_rows_normed with the kind of norm as an argument: rms != 0: y = x / sqrt(mean(x^2) + eps) * (gain + gain_offset) + offset. */
+int lb_gemm_rows_normed_kind(int out_dtype, const float* x, int64_t ldx, const float* gain, const float* offset, float eps, int rms, float gain_offset,
+                             const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N,
+                             int K, int act, void* kv_cache, const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size,
+                             void* stream);
 /* lb_rms_groups with `gain_offset` added to every gain (1 for gains stored around zero). */
 int lb_rms_groups_offset(int out_dtype, const float* x, int64_t ldx, const int32_t* rows, const float* weight, float gain_offset, void* y, int64_t ldy,
                          int n_rows, int width, int groups, float eps, void* stream);

@@ -69,6 +69,8 @@ struct RowNorm {
     const float* gain;
     const float* offset;
     float eps;
+    int rms;                  // non-zero: no mean is taken off (an RMS norm); gain_offset is added to every gain
+    float gain_offset;
 };
 
 __device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bfloat16* act, int ld, int k_pad) {
@@ -80,6 +82,12 @@ __device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bflo
     for (int j = 0; j < kVecs; ++j) {              // weights: asked for before the kernel before this one has ended
         const int i = lane + 32 * j;
         gain[j] = (i < n_vec && n.gain != nullptr) ? __ldg(reinterpret_cast<const float4*>(n.gain) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        if (n.gain != nullptr) {
+            gain[j].x += n.gain_offset;
+            gain[j].y += n.gain_offset;
+            gain[j].z += n.gain_offset;
+            gain[j].w += n.gain_offset;
+        }
         offs[j] = (i < n_vec && n.offset != nullptr) ? __ldg(reinterpret_cast<const float4*>(n.offset) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     lb_wait_for_predecessor();
@@ -100,7 +108,7 @@ __device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bflo
         float sum = 0.0f;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-        const float mean = lb_warp_sum(sum) / (float)K;
+        const float mean = n.rms ? 0.0f : lb_warp_sum(sum) / (float)K;
         float ss = 0.0f;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
@@ -352,6 +360,16 @@ extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, c
                                    const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr, void* out,
                                    int64_t ldo, int M, int N, int K, int act, void* kv_cache, const int32_t* slot_mapping, int q_dim,
                                    int n_kv_head, int head_dim, int page_size, void* stream) {
+    return lb_gemm_rows_normed_kind(out_dtype, x, ldx, gain, offset, eps, 0, 0.0f, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv_cache,
+                                    slot_mapping, q_dim, n_kv_head, head_dim, page_size, stream);
+}
+
+// The same with the kind of norm as an argument: rms != 0 divides by sqrt(mean(x^2) + eps) without taking a mean off, and gain_offset is
+// added to every gain.
+extern "C" int lb_gemm_rows_normed_kind(int out_dtype, const float* x, int64_t ldx, const float* gain, const float* offset, float eps, int rms,
+                                        float gain_offset, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
+                                        void* out, int64_t ldo, int M, int N, int K, int act, void* kv_cache, const int32_t* slot_mapping,
+                                        int q_dim, int n_kv_head, int head_dim, int page_size, void* stream) {
     LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows_normed: unknown output dtype %d", out_dtype);
     if (!lb_gemm_rows_normed_supports(x, ldx, W, ldw, M, N, K) || ((uintptr_t)gain & 15) != 0 || ((uintptr_t)offset & 15) != 0)
         return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows_normed: takes 1 to 16 tokens, K up to 1024 and a multiple of 8, 16-byte aligned bases "
@@ -369,7 +387,7 @@ extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, c
                          q_dim + 2 * n_kv_head * head_dim == N,
                      "gemm_rows_normed: the cache destination needs N = q_dim + 2 * n_kv_head * head_dim (N=%d q_dim=%d heads %d x %d)", N,
                      q_dim, n_kv_head, head_dim);
-    const RowNorm norm{x, ldx, gain, offset, eps};
+    const RowNorm norm{x, ldx, gain, offset, eps, rms, gain_offset};
     auto s = static_cast<cudaStream_t>(stream);
     if (out_dtype == LB_F32)
         return launch<1, 4, float, 2>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);

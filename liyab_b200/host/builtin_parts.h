@@ -186,7 +186,7 @@ public:
         a.page_size = view->group->page_size;
         const kernels::KvDestination dest{cache, view->slot_mapping, q_dim, a.n_kv_head, a.head_dim, a.page_size};
         kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, qkv.weight, qkv.bias, qkv_out, T, kernels::kNone,
-                                  nullptr, &dest);
+                                  nullptr, &dest, norm.rms, norm.gain_offset);
         attend_and_project(ctx, qkv_out, cache, *view, a, x);
         return true;
     }
@@ -280,7 +280,8 @@ public:
         const int T = ctx.n_tokens;
         if (xielu != nullptr || !kernels::gemm_rows_normed_supports(ctx.runtime, x_in, up.weight, T)) return false;
         const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
-        kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, up.weight, up.bias, mid, T, activation, nullptr, nullptr);
+        kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, up.weight, up.bias, mid, T, activation, nullptr, nullptr, norm.rms,
+                                  norm.gain_offset);
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
         return true;
     }

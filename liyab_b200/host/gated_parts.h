@@ -121,8 +121,18 @@ public:
     bool capturable() const override { return true; }
     std::optional<KvNeed> kv_need() const override { return KvNeed{G, shape.head_dim, shape.chunk > 0 ? shape.chunk : shape.window}; }
 
-    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, h, x, &x, unit); }
-    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, h, y, nullptr, unit); }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, &h, nullptr, nullptr, x, &x, unit); }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, &h, nullptr, nullptr, y, nullptr, unit); }
+    // A step of up to 16 tokens in bfloat16: the projection normalises the rows itself.
+    bool normalises(const StepContext& ctx, const Rows& x_in) const override { return kernels::gemm_rows_normed_supports(ctx.runtime, x_in, proj.weight, ctx.n_tokens); }
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) override {
+        if (!normalises(ctx, x_in)) return false;
+        run(ctx, nullptr, &x_in, &norm, x, &x, unit);
+        return true;
+    }
+    void forward_from_into(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& y, CacheUnit unit) override {
+        run(ctx, nullptr, &x_in, &norm, y, nullptr, unit);
+    }
 
     kernels::AttentionShape shape;
     int64_t hidden = 0;
@@ -135,13 +145,16 @@ public:
 
 private:
     int64_t qkv_cols() const { return static_cast<int64_t>(H) * D + static_cast<int64_t>(G) * (D + E); }
-    void run(StepContext& ctx, const Rows& h, const Rows& y, const Rows* residual, CacheUnit unit) {
+    // Either the normalised rows h, or the stream's rows x_in with the recipe of the norm before the mixer.
+    void run(StepContext& ctx, const Rows* h, const Rows* x_in, const NormRecipe* norm, const Rows& y, const Rows* residual, CacheUnit unit) {
         const int T = ctx.n_tokens, P = shape.head_dim;
         const DType dt = ctx.runtime.dtype;
         Workspace& ws = *ctx.workspace;
         cudaStream_t s = ctx.stream();
         const Rows pr = ws.get("gated_attention.proj", T, proj.weight.dim(0), DType::F32);
-        kernels::linear(ctx.runtime, &ws, h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        if (h != nullptr) kernels::linear(ctx.runtime, &ws, *h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        else kernels::gemm_rows_normed(s, *x_in, norm->gain, norm->offset, norm->eps, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr, nullptr, norm->rms,
+                                       norm->gain_offset);
         const GroupView* view = nullptr;
         void* cache = ctx.kv(unit.read, &view);
         kernels::AttentionShape a = shape;
@@ -217,8 +230,17 @@ public:
     }
     bool capturable() const override { return true; }
     std::optional<StateNeed> state_need() const override { return StateNeed{{m.slot_floats()}, DType::F32}; }
-    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, h, x, &x, unit); }
-    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, h, y, nullptr, unit); }
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, &h, nullptr, nullptr, x, &x, unit); }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, &h, nullptr, nullptr, y, nullptr, unit); }
+    bool normalises(const StepContext& ctx, const Rows& x_in) const override { return kernels::gemm_rows_normed_supports(ctx.runtime, x_in, proj.weight, ctx.n_tokens); }
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) override {
+        if (!normalises(ctx, x_in)) return false;
+        run(ctx, nullptr, &x_in, &norm, x, &x, unit);
+        return true;
+    }
+    void forward_from_into(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& y, CacheUnit unit) override {
+        run(ctx, nullptr, &x_in, &norm, y, nullptr, unit);
+    }
 
     // Portions of this many rows or more go through the kernel that works in pieces.
     static constexpr int kChunkedFrom = 16;
@@ -232,13 +254,15 @@ public:
 
 private:
     int64_t gate_at() const { return 2 * static_cast<int64_t>(m.n_head) * (m.dim + m.vdim); }
-    void run(StepContext& ctx, const Rows& h, const Rows& y, const Rows* residual, CacheUnit unit) {
+    void run(StepContext& ctx, const Rows* h, const Rows* x_in, const NormRecipe* norm, const Rows& y, const Rows* residual, CacheUnit unit) {
         if (!unit.write) throw invalid_model("matrix_memory: a memory is carried by the run that owns it; the run order lets another read it");
         const int T = ctx.n_tokens, H = m.n_head, D = m.dim, E = m.vdim;
         Workspace& ws = *ctx.workspace;
         cudaStream_t s = ctx.stream();
         const Rows pr = ws.get("matrix_memory.proj", T, proj.weight.dim(0), DType::F32);
-        kernels::linear(ctx.runtime, &ws, h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        if (h != nullptr) kernels::linear(ctx.runtime, &ws, *h, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr);
+        else kernels::gemm_rows_normed(s, *x_in, norm->gain, norm->offset, norm->eps, proj.weight, bias.get(s), pr, T, kernels::kNone, nullptr, nullptr, norm->rms,
+                                       norm->gain_offset);
         const int64_t HD = static_cast<int64_t>(H) * D, HE = static_cast<int64_t>(H) * E;
         const Rows q = pr.columns(0, HD), k = pr.columns(HD, HD), v = pr.columns(2 * HD, HE), g = pr.columns(2 * HD + HE, HE);
         const Rows zi = pr.columns(gate_at(), H), zf = pr.columns(gate_at() + H, H);
@@ -306,20 +330,35 @@ public:
             if (const auto n = b->state_need()) return n;
         return std::nullopt;
     }
-    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override {
-        std::vector<Rows> ys;
-        for (size_t i = 0; i < branches.size(); ++i) {
-            ys.push_back(ctx.workspace->get(std::format("branch_sum.{}", i), ctx.n_tokens, size, DType::F32));
-            branches[i]->forward_into(ctx, h, ys.back(), unit);
-            ctx.tap("branch." + names[i], ys.back());
-        }
-        kernels::rms_sum_add(ctx.stream(), x, ys, gains, ctx.n_tokens, scale, eps);
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, &h, nullptr, nullptr, x, unit); }
+    // Where every branch can normalise the rows itself for this step, the norm before the mixer is not launched.
+    bool normalises(const StepContext& ctx, const Rows& x_in) const override {
+        for (const auto& b : branches)
+            if (!b->normalises(ctx, x_in)) return false;
+        return true;
+    }
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) override {
+        if (!normalises(ctx, x_in)) return false;
+        run(ctx, nullptr, &x_in, &norm, x, unit);
+        return true;
     }
     int64_t size;
     float scale, eps;
     std::vector<std::string> names;
     std::vector<std::shared_ptr<Mixer>> branches;
     std::vector<const float*> gains;
+
+private:
+    void run(StepContext& ctx, const Rows* h, const Rows* x_in, const NormRecipe* norm, const Rows& x, CacheUnit unit) {
+        std::vector<Rows> ys;
+        for (size_t i = 0; i < branches.size(); ++i) {
+            ys.push_back(ctx.workspace->get(std::format("branch_sum.{}", i), ctx.n_tokens, size, DType::F32));
+            if (h != nullptr) branches[i]->forward_into(ctx, *h, ys.back(), unit);
+            else branches[i]->forward_from_into(ctx, *x_in, *norm, ys.back(), unit);
+            ctx.tap("branch." + names[i], ys.back());
+        }
+        kernels::rms_sum_add(ctx.stream(), x, ys, gains, ctx.n_tokens, scale, eps);
+    }
 };
 
 // ---- the gated feed-forward: down(gate(W_gate h) * (W_up h)) ------------------------------------------------------

@@ -90,8 +90,8 @@ bool gemm_rows_normed_supports(const Runtime& rt, const Rows& x, const Tensor& w
 }
 
 void gemm_rows_normed(cudaStream_t s, const Rows& x, const float* gain, const float* offset, float eps, const Tensor& w, const float* bias,
-                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv) {
-    check(lb_gemm_rows_normed(code(out.dtype, "out"), x.f32(), x.stride, gain, offset, eps, w.data, w.dim(1), bias,
+                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv, bool rms, float gain_offset) {
+    check(lb_gemm_rows_normed_kind(code(out.dtype, "out"), x.f32(), x.stride, gain, offset, eps, rms ? 1 : 0, gain_offset, w.data, w.dim(1), bias,
                               residual ? residual->f32() : nullptr, residual ? residual->stride : 0, out.data, out.stride, m,
                               static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1)), act, kv ? kv->cache : nullptr,
                               kv ? kv->slot_mapping : nullptr, kv ? kv->q_dim : 0, kv ? kv->n_kv_head : 0, kv ? kv->head_dim : 0,

@@ -60,10 +60,11 @@ inline constexpr int kRowsMaxK = 1024;
 bool gemm_rows_takes(int m, int n, int k, int sm_count);
 bool gemm_rows_supports(const Rows& a, const Tensor& w, int m);
 // The same product with the rows of the float32 matrix x normalised inside the kernel (LayerNorm: gain, offset or
-// null, eps): up to 16 tokens, K up to 1024, bfloat16 weights.
+// null, eps; with `rms` no mean is taken off and gain_offset is added to every gain): up to 16 tokens, K up to 1024,
+// bfloat16 weights.
 bool gemm_rows_normed_supports(const Runtime& rt, const Rows& x, const Tensor& w, int m);
 void gemm_rows_normed(cudaStream_t s, const Rows& x, const float* gain, const float* offset, float eps, const Tensor& w, const float* bias,
-                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv);
+                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv, bool rms = false, float gain_offset = 0.0f);
 void gemm_rows(cudaStream_t s, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m, int act,
                const Rows* residual, const KvDestination* kv);
 int gemm_persistent_tile(const Rows& a, const Tensor& w, const Rows& out, int m, const Rows* residual);

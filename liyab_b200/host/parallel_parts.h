@@ -28,6 +28,11 @@ public:
     void forward(StepContext& ctx, const Rows& x, const Rows& out, int n_rows, const int32_t* rows) override {
         kernels::rms_groups(ctx.stream(), x, rows, weight, out, n_rows, groups, eps, gain_offset);
     }
+    // One group: the part after the norm may normalise the rows itself (a projection of a few tokens does).
+    std::optional<NormRecipe> recipe() const override {
+        if (groups != 1) return std::nullopt;
+        return NormRecipe{weight, nullptr, eps, true, gain_offset};
+    }
     int64_t size;
     int groups;
     float eps;

@@ -135,12 +135,15 @@ public:
 };
 
 // What a norm may hand to the part after it instead of its output: the recipe of a LayerNorm with 32-bit two-pass
-// statistics, y = (x - mean) / sqrt(var + eps) * gain + offset (gain and offset may be null).  A part that can apply
+// statistics, y = (x - mean) / sqrt(var + eps) * gain + offset (gain and offset may be null), or, with `rms`, of an RMS
+// norm over the whole row, y = x / sqrt(mean(x^2) + eps) * (gain + gain_offset).  A part that can apply
 // it while it reads its input (a projection of a few tokens normalises the rows inside its kernel) saves the launch.
 struct NormRecipe {
     const float* gain = nullptr;
     const float* offset = nullptr;
     float eps = 0.0f;
+    bool rms = false;
+    float gain_offset = 0.0f;
 };
 
 class Norm : public Part {
@@ -173,6 +176,13 @@ public:
     // The same from the un-normalised rows `x_in` (float32) and the norm's recipe; false (and nothing done) where the
     // mixer cannot apply the recipe itself for this step.
     virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) { return false; }
+    // Whether the mixer can apply a norm's recipe itself for this step (forward_from would not decline), and the same as
+    // forward_into: the output to `out` from the un-normalised rows.  A mixer that is a branch of another is asked the first
+    // before it is given the second.
+    virtual bool normalises(const StepContext& ctx, const Rows& x_in) const { return false; }
+    virtual void forward_from_into(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& out, CacheUnit unit) {
+        throw internal_error("this mixer does not normalise its input itself");
+    }
 };
 
 class FeedForward : public Part {
