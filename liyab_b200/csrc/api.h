@@ -320,6 +320,14 @@ int lb_matrix_memory(const float* q, const float* k, const float* v, const float
                      int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale, float k_scale, float cap, int chunked,
                      void* stream);
 
+/* The same for steps with long portions, every piece of 32 rows a block of its own (three launches: the pieces' own sums, a scan over them,
+ * the pieces' outputs); scratch: lb_matrix_memory_pieces_floats(..) floats. */
+int64_t lb_matrix_memory_pieces_floats(int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile);
+int lb_matrix_memory_pieces(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                            const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                            int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile,
+                            float q_scale, float k_scale, float cap, float* scratch, void* stream);
+
 /* Routed experts (see routed_experts.cu).  ids and weights: [rows, top]. */
 int lb_router_topk(int dtype, const void* h, int64_t ldh, const void* router, int32_t* ids, float* weights, int n_rows, int n_experts, int width, int top,
                    int softmax, int renormalise, void* stream);

@@ -13,6 +13,7 @@
 // State of a request: [head][value tile][D x VT | D | 1] floats (S for the tile's VT value columns, n, m); every tile
 // keeps its own n and m, so that the blocks of a launch share nothing.
 //
+// lb_matrix_memory_pieces is the form for long prompts: every piece a block of its own, in three launches (see the kernels).
 // lb_matrix_memory walks a request's rows one after the other (a block per (request, head, value tile)); a decode step
 // is one such row.  With `chunked` it does the same in pieces of 32 rows: inside a piece the rows' sums are products of
 // small matrices (scores q_t . k_j weighted by the decay between j and t, then the values), and the state moves once per
@@ -43,6 +44,27 @@ struct MemoryArgs {
     int H, D, E, VT, NV, rot_dims;
     float q_scale, k_scale, cap;
 };
+
+// Scratch of the three-launch form for long prompts, in which every piece of 32 rows is a block of its own.
+struct PieceArgs {
+    float* sums;        // [piece][head][tile][D * VT + D]: a piece's own sum; after the scan, the state before the piece
+    float* scalars;     // [piece][head][2]: the piece's sum of log forget gates, and the maximum its own rows would reach from minus infinity
+    float* before;      // [piece][head]: the running maximum before the piece
+};
+
+// Piece g of the step (pieces of 32 rows, request after request): its request and its number inside the request; false past the last.
+__device__ __forceinline__ bool find_piece(const int32_t* q_start, int n_seq, int g, int* seq, int* piece) {
+    for (int s = 0; s < n_seq; ++s) {
+        const int pieces = (q_start[s + 1] - q_start[s] + 31) >> 5;
+        if (g < pieces) {
+            *seq = s;
+            *piece = g;
+            return true;
+        }
+        g -= pieces;
+    }
+    return false;
+}
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -205,14 +227,20 @@ __device__ __forceinline__ void state_after_piece(float* S, const float* ks, con
 // (three round trips to memory a piece instead of three a row); thread (c, g) owns column c of the tile for rows g, g + DS, ..
 constexpr int kPiece = 32;
 
-template <int VTP, int NT>
-__global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) {
+// MODE 0: a block walks a request's pieces one after the other from the state in its slot.  For long prompts three launches instead:
+// MODE 1, a block per piece: the piece's own sum, as if its state began at zero and its maximum at minus infinity; then the scan
+// (matrix_memory_scan_kernel) leaves the state before every piece in the sum's place; MODE 2, a block per piece: the piece's outputs
+// from that state.
+template <int VTP, int NT, int MODE>
+__global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, PieceArgs w, int n_seq) {
     constexpr int vt_pow2 = VTP, DS = NT / VTP, R = kPiece / DS, kWarps = NT / 32;      // thread (c, tg) owns column c for the R rows tg, tg + DS, ..
     extern __shared__ float smem[];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
-    const int seq = blockIdx.x, h = blockIdx.y, nv = blockIdx.z;
-    const int row0 = a.q_start[seq], row1 = a.q_start[seq + 1];
+    const int h = blockIdx.y, nv = blockIdx.z;
+    int seq = blockIdx.x, piece = 0;
+    if (MODE != 0 && !find_piece(a.q_start, n_seq, blockIdx.x, &seq, &piece)) return;
+    const int row0 = a.q_start[seq] + piece * kPiece, row1 = MODE == 0 ? a.q_start[seq + 1] : min(a.q_start[seq + 1], row0 + kPiece);
     if (row1 <= row0) return;
     const int D = a.D, VT = a.VT, E = a.E, LDQ = D + 1, LDP = kPiece + 1;
     const int c = threadIdx.x & (vt_pow2 - 1), tg = threadIdx.x / vt_pow2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,11 +261,18 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) 
     float* den = uj + kPiece;              // what divides row t
     float* sc = den + kPiece;              // [0] the old state's factor in the new one, [1] m_last
     int* pos_s = reinterpret_cast<int*>(sc + 2);      // the rows' positions
-    float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1);
     const bool gated = a.decay == nullptr;
     const float logd = gated ? 0.0f : logf(a.decay[h]);       // -inf for a decay of 0: exp gives 0
-    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) S[i] = st[i];
-    float m = st[(size_t)D * VT + D];
+    float* st = MODE == 0 ? a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1)
+                          : w.sums + (((size_t)blockIdx.x * a.H + h) * a.NV + nv) * ((size_t)D * VT + D);
+    float m;
+    if (MODE == 1) {
+        for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) S[i] = 0.0f;
+        m = gated ? -CUDART_INF_F : 0.0f;
+    } else {
+        for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) S[i] = st[i];
+        m = MODE == 0 ? st[(size_t)D * VT + D] : w.before[(size_t)blockIdx.x * a.H + h];
+    }
     for (int p0 = row0; p0 < row1; p0 += kPiece) {
         const int n = min(kPiece, row1 - p0);
         // The piece's rows as they are, all asked for at once (4-byte cp.async, one round trip), and the gates.
@@ -321,9 +356,14 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) 
             if (t == 0) {
                 sc[0] = gated ? expf(gb[n - 1] + m - gm[n - 1]) : expf((float)n * logd);
                 sc[1] = gated ? gm[n - 1] : 0.0f;
+                if (MODE == 1 && nv == 0) {
+                    w.scalars[((size_t)blockIdx.x * a.H + h) * 2] = gated ? gb[n - 1] : (float)n * logd;
+                    w.scalars[((size_t)blockIdx.x * a.H + h) * 2 + 1] = sc[1];
+                }
             }
         }
         // Weighted scores: a warp per row t, lane j.
+        if (MODE != 1)
         for (int t = warp; t < kPiece; t += kWarps) {
             const int j = lane;
             float p = 0.0f;
@@ -358,7 +398,7 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) 
         __syncthreads();
         const float m_next = sc[1];
         // Outputs: this thread's rows tg, tg + DS, .. (up to eight) of column c.
-        {
+        if (MODE != 1) {
             float from_state[R], from_piece[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) from_state[r] = from_piece[r] = 0.0f;
@@ -384,6 +424,7 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) 
         }
         __syncthreads();
         // The state after the piece.
+        if (MODE == 2) break;
         const float keep = sc[0];
         if (D <= 2 * DS) state_after_piece<2, DS>(S, ks, vs, uj, keep, tg, c, cc, live, n, D, VT, LDQ);
         else if (D <= 4 * DS) state_after_piece<4, DS>(S, ks, vs, uj, keep, tg, c, cc, live, n, D, VT, LDQ);
@@ -397,16 +438,78 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a) 
         m = m_next;
         __syncthreads();
     }
-    for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) st[i] = S[i];
-    if (threadIdx.x == 0) st[(size_t)D * VT + D] = m;
+    if constexpr (MODE != 2) {
+        for (int i = threadIdx.x; i < D * VT + D; i += blockDim.x) st[i] = S[i];
+        if (MODE == 0 && threadIdx.x == 0) st[(size_t)D * VT + D] = m;
+    }
+}
+
+// The scan between the two launches of the per-piece form: a block per (request, head, value tile) walks the request's pieces.  With
+// (b, m_own) the piece's scalars: m_new = max(b + m, m_own), S_new = exp(b + m - m_new) S + exp(m_own - m_new) sum; a fixed decay has
+// m = 0 throughout and b = rows x log(decay).  The state before the piece takes the sum's place; the next piece's sum travels (cp.async)
+// while this one is added.
+__global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryArgs a, PieceArgs w) {
+    extern __shared__ float smem[];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int seq = blockIdx.x, h = blockIdx.y, nv = blockIdx.z;
+    const int len = a.q_start[seq + 1] - a.q_start[seq], pieces = (len + 31) >> 5;
+    if (pieces <= 0) return;
+    int g0 = 0;
+    for (int s = 0; s < seq; ++s) g0 += (a.q_start[s + 1] - a.q_start[s] + 31) >> 5;
+    const int count = a.D * a.VT + a.D;
+    float* S = smem;                    // [count]
+    float* buf = S + count;             // [2][count]
+    float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)count + 1);
+    const bool gated = a.decay == nullptr;
+    auto sum_of = [&](int g) { return w.sums + (((size_t)g * a.H + h) * a.NV + nv) * (size_t)count; };
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        cp_async4(S + i, st + i);
+        cp_async4(buf + i, sum_of(g0) + i);
+    }
+    cp_async_commit();
+    float m = st[count];
+    for (int p = 0; p < pieces; ++p) {
+        const int g = g0 + p;
+        float* mine = buf + (p & 1) * count;
+        cp_async_wait_all();
+        __syncthreads();
+        if (p + 1 < pieces) {
+            float* next = buf + ((p + 1) & 1) * count;
+            for (int i = threadIdx.x; i < count; i += blockDim.x) cp_async4(next + i, sum_of(g + 1) + i);
+        }
+        cp_async_commit();
+        const float b = w.scalars[((size_t)g * a.H + h) * 2], m_own = w.scalars[((size_t)g * a.H + h) * 2 + 1];
+        const float m_new = gated ? fmaxf(b + m, m_own) : 0.0f;
+        const float keep = gated ? expf(b + m - m_new) : expf(b), take = gated ? expf(m_own - m_new) : 1.0f;
+        float* out = sum_of(g);
+        for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            const float before = S[i];
+            out[i] = before;
+            S[i] = fmaf(keep, before, take * mine[i]);
+        }
+        if (nv == 0 && threadIdx.x == 0) w.before[(size_t)g * a.H + h] = m;
+        m = m_new;
+    }
+    for (int i = threadIdx.x; i < count; i += blockDim.x) st[i] = S[i];
+    if (threadIdx.x == 0) st[count] = m;
 }
 
 }  // namespace
 
-extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
-                                const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
-                                int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
-                                float k_scale, float cap, int chunked, void* stream) {
+namespace {
+struct PieceScratch {
+    float* sums;
+    float* scalars;
+    float* before;
+    int max_pieces;
+};
+}  // namespace
+
+static int matrix_memory_run(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                             const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                             int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
+                             float k_scale, float cap, int chunked, const PieceScratch* pieces, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_head > 0 && dim > 0 && vdim > 0 && value_tile > 0 && value_tile <= 64, "matrix memory: bad sizes heads=%d dim=%d vdim=%d tile=%d",
                  n_head, dim, vdim, value_tile);
     LB_CHECK_ARG((decay != nullptr) != (zi != nullptr && zf != nullptr), "matrix memory: either a fixed decay or the two gates");
@@ -425,19 +528,55 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
         const size_t bytes = ((size_t)dim * value_tile + dim + 2 * (size_t)kPiece * (dim + 1) + (size_t)kPiece * value_tile + kPiece * (kPiece + 1) + 7 * kPiece + 2) *
                              sizeof(float);
         LB_CHECK_ARG(bytes <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
-        auto launch = [&](auto kernel, int threads) -> int {
+        auto launch = [&](auto kernel, int threads, int blocks, const PieceArgs& w) -> int {
             if (bytes > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-            LB_CHECK_CUDA(lb_launch_overlapped(kernel, dim3(n_seq, n_head, a.NV), dim3(threads), bytes, s, a));
+            LB_CHECK_CUDA(lb_launch_overlapped(kernel, dim3(blocks, n_head, a.NV), dim3(threads), bytes, s, a, w, n_seq));
             return LB_OK;
         };
-        if (p2 <= 8) return launch(matrix_memory_chunks_kernel<8, 256>, 256);
-        if (p2 == 16) return launch(matrix_memory_chunks_kernel<16, 512>, 512);
-        if (p2 == 32) return launch(matrix_memory_chunks_kernel<32, 512>, 512);
-        return launch(matrix_memory_chunks_kernel<64, 512>, 512);
+#define LB_MEMORY_MODE(MODE, blocks, w)                                                                   \
+    (p2 <= 8    ? launch(matrix_memory_chunks_kernel<8, 256, MODE>, 256, blocks, w)                      \
+     : p2 == 16 ? launch(matrix_memory_chunks_kernel<16, 512, MODE>, 512, blocks, w)                     \
+     : p2 == 32 ? launch(matrix_memory_chunks_kernel<32, 512, MODE>, 512, blocks, w)                     \
+                : launch(matrix_memory_chunks_kernel<64, 512, MODE>, 512, blocks, w))
+        if (pieces == nullptr) return LB_MEMORY_MODE(0, n_seq, PieceArgs{});
+        // Every piece a block of its own: the pieces' own sums, the scan over them, the pieces' outputs.
+        const PieceArgs w{pieces->sums, pieces->scalars, pieces->before};
+        if (int rc = LB_MEMORY_MODE(1, pieces->max_pieces, w)) return rc;
+        const size_t scan_bytes = 3 * ((size_t)dim * value_tile + dim) * sizeof(float);
+        LB_CHECK_ARG(scan_bytes <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
+        if (scan_bytes > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)scan_bytes));
+        LB_CHECK_CUDA(lb_launch_overlapped(matrix_memory_scan_kernel, dim3(n_seq, n_head, a.NV), dim3(256), scan_bytes, s, a, w));
+        return LB_MEMORY_MODE(2, pieces->max_pieces, w);
+#undef LB_MEMORY_MODE
     }
     const size_t smem = ((size_t)dim * value_tile + 3 * (size_t)dim + 256 + 2 * (2 * (size_t)dim + value_tile)) * sizeof(float);
     LB_CHECK_ARG(smem <= 200 * 1024, "matrix memory: a tile of %d x %d floats does not fit shared memory", dim, value_tile);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LB_CHECK_CUDA(lb_launch_overlapped(matrix_memory_rows_kernel, dim3(n_seq, n_head, a.NV), dim3(256), smem, s, a, p2));
     return LB_OK;
+}
+
+extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                                int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
+                                float k_scale, float cap, int chunked, void* stream) {
+    return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
+                             value_tile, q_scale, k_scale, cap, chunked, nullptr, stream);
+}
+
+extern "C" int64_t lb_matrix_memory_pieces_floats(int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile) {
+    const int64_t pieces = n_tokens / 32 + n_seq, tiles = (vdim + value_tile - 1) / value_tile;
+    return pieces * n_head * (tiles * ((int64_t)dim * value_tile + dim) + 3);
+}
+
+extern "C" int lb_matrix_memory_pieces(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                       const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
+                                       float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim,
+                                       int value_tile, float q_scale, float k_scale, float cap, float* scratch, void* stream) {
+    LB_CHECK_ARG(scratch != nullptr && n_tokens >= 0 && value_tile > 0, "matrix memory in pieces: no scratch");
+    const int64_t pieces = n_tokens / 32 + n_seq, tiles = (vdim + value_tile - 1) / value_tile;
+    const int64_t sums = pieces * n_head * tiles * ((int64_t)dim * value_tile + dim);
+    const PieceScratch ps{scratch, scratch + sums, scratch + sums + pieces * n_head * 2, (int)pieces};
+    return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
+                             value_tile, q_scale, k_scale, cap, 1, &ps, stream);
 }

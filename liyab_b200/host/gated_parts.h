@@ -244,6 +244,8 @@ public:
 
     // Portions of this many rows or more go through the kernel that works in pieces.
     static constexpr int kChunkedFrom = 16;
+    // Steps whose longest portion has this many rows or more take the three-launch form (a block per piece).
+    static constexpr int kPiecesFrom = 128;
     kernels::MemoryShape m;
     int64_t hidden = 0;
     bool gated = false, head_norm = true;
@@ -267,9 +269,18 @@ private:
         const Rows q = pr.columns(0, HD), k = pr.columns(HD, HD), v = pr.columns(2 * HD, HE), g = pr.columns(2 * HD + HE, HE);
         const Rows zi = pr.columns(gate_at(), H), zf = pr.columns(gate_at() + H, H);
         const Rows o = ws.get("matrix_memory.o", T, HE, DType::F32);
-        kernels::matrix_memory(s, q, k, v, gated ? &zi : nullptr, gated ? &zf : nullptr, gated ? nullptr : decay.get(s), m.rot_dims > 0 ? freq.get(s) : nullptr,
-                               ctx.positions, ctx.q_start, ctx.state_slots, static_cast<float*>(ctx.state(unit.read)), o, ctx.n_seq, m,
-                               ctx.max_q_len >= kChunkedFrom);
+        const float* decays = gated ? nullptr : decay.get(s);
+        const float* freqs = m.rot_dims > 0 ? freq.get(s) : nullptr;
+        float* state = static_cast<float*>(ctx.state(unit.read));
+        if (ctx.max_q_len >= kPiecesFrom) {
+            // Long portions: every piece of 32 rows a block of its own, so that a few requests fill the GPU.
+            float* scratch = static_cast<float*>(ws.flat("matrix_memory.pieces", kernels::memory_pieces_floats(T, ctx.n_seq, m), DType::F32));
+            kernels::matrix_memory_pieces(s, q, k, v, gated ? &zi : nullptr, gated ? &zf : nullptr, decays, freqs, ctx.positions, ctx.q_start, ctx.state_slots, state,
+                                          o, T, ctx.n_seq, m, scratch);
+        } else {
+            kernels::matrix_memory(s, q, k, v, gated ? &zi : nullptr, gated ? &zf : nullptr, decays, freqs, ctx.positions, ctx.q_start, ctx.state_slots, state, o,
+                                   ctx.n_seq, m, ctx.max_q_len >= kChunkedFrom);
+        }
         ctx.tap("memory", o);
         const Rows heads = ws.get("matrix_memory.heads", T, HE, ctx.runtime.dtype);
         kernels::head_gate(s, o, E, g, norm_gain, heads, T, H, E, head_norm, gate, eps);

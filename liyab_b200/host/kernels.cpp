@@ -340,6 +340,22 @@ void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, 
                            m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, s), "matrix_memory");
 }
 
+int64_t memory_pieces_floats(int n_tokens, int n_seq, const MemoryShape& m) {
+    return lb_matrix_memory_pieces_floats(n_tokens, n_seq, m.n_head, m.dim, m.vdim, m.value_tile);
+}
+
+void matrix_memory_pieces(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
+                          const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_tokens, int n_seq,
+                          const MemoryShape& m, float* scratch) {
+    if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
+        (zf != nullptr && zf->stride != q.stride))
+        throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
+    check(lb_matrix_memory_pieces(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
+                                  m.rot_dims, positions, q_start, slots, state, m.slot_floats(), out.f32(), out.stride, n_tokens, n_seq, m.n_head, m.dim,
+                                  m.vdim, m.value_tile, m.q_scale, m.k_scale, m.cap, scratch, s), "matrix_memory_pieces");
+    launches.fetch_add(2, std::memory_order_relaxed);
+}
+
 void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise) {
     if (router.shape.size() != 2 || router.dim(1) != h.cols || router.dtype != h.dtype) throw invalid_argument("router: the matrix does not fit the rows");
     check(lb_router_topk(code(h.dtype, "h"), h.data, h.stride, router.data, ids, weights, n_rows, static_cast<int>(router.dim(0)), static_cast<int>(h.cols), top,

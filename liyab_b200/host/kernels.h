@@ -195,6 +195,11 @@ int memory_value_tile(int dim, int vdim);
 void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
                    const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_seq, const MemoryShape& m,
                    bool chunked);
+// The form for long portions (every piece of 32 rows a block of its own, three launches); `scratch` holds memory_pieces_floats(..) floats.
+int64_t memory_pieces_floats(int n_tokens, int n_seq, const MemoryShape& m);
+void matrix_memory_pieces(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
+                          const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_tokens, int n_seq,
+                          const MemoryShape& m, float* scratch);
 
 // ---- routed experts ----
 void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise);

@@ -606,6 +606,7 @@ for _name, _args in {
     "lb_head_gate": [_i, _i, _p, _l, _i, _p, _l, _p, _p, _l, _i, _i, _i, _i, _i, _f, _p],
     "lb_gated_act": [_i, _p, _l, _p, _l, _i, _i, _i, _p],
     "lb_matrix_memory": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _p],
+    "lb_matrix_memory_pieces": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _p],
     "lb_router_topk": [_i, _p, _l, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "lb_expert_plan": [_p, _i, _i, _p, _p, _p, _p],
     "lb_expert_product": [_i, _i, _p, _l, _p, _l, _p, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
@@ -682,6 +683,24 @@ def matrix_memory(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off
                                  _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32), state.stride(0), _dev(out, "out", torch.float32),
                                  out.stride(0), q_start.numel() - 1, n_head, dim, vdim, value_tile, float(q_scale), float(k_scale), float(cap), int(chunked),
                                  stream_ptr()), "matrix_memory")
+    return out
+
+
+def matrix_memory_pieces(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
+                         freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+                         out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float) -> torch.Tensor:
+    """matrix_memory in its form for long portions: every piece of 32 rows a block of its own (three launches)."""
+    base = _dev(proj, "proj", torch.float32)
+    at = lambda off: None if off is None else base + 4 * off
+    T, S = proj.shape[0], q_start.numel() - 1
+    fn = lib().lb_matrix_memory_pieces_floats
+    fn.argtypes, fn.restype = [_i] * 6, _c.c_int64
+    scratch = torch.empty(int(fn(T, S, n_head, dim, vdim, value_tile)), dtype=torch.float32, device=proj.device)
+    check(lib().lb_matrix_memory_pieces(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+                                        _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32),
+                                        _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32),
+                                        state.stride(0), _dev(out, "out", torch.float32), out.stride(0), T, S, n_head, dim, vdim, value_tile, float(q_scale),
+                                        float(k_scale), float(cap), _dev(scratch, "scratch"), stream_ptr()), "matrix_memory_pieces")
     return out
 
 

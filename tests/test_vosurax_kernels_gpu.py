@@ -132,7 +132,7 @@ def plain_memory(q, k, v, zi, zf, decay, cap, S, nvec, m):
 @pytest.mark.parametrize("H,D,E,tile", [(2, 16, 24, 24), (3, 10, 70, 24), (1, 64, 128, 32), (2, 6, 5, 5), (1, 20, 130, 64), (2, 1, 1, 1)])
 def test_matrix_memories_row_by_row_and_in_pieces(gated, H, D, E, tile):
     """Three requests of unequal length in one launch, each in several steps cut anywhere, through slots in scrambled order; every step once row by
-    row and once in pieces, from the same state; rotation of part of a head; against the plain recurrence in float64."""
+    row, once in pieces and once with every piece a block of its own, from the same state; rotation of part of a head; against the plain recurrence in float64."""
     import torch
     from liyab_b200 import ops
     rng = np.random.default_rng(7 * H + D)
@@ -145,7 +145,7 @@ def test_matrix_memories_row_by_row_and_in_pieces(gated, H, D, E, tile):
     cap, qs, ks = 7.0, D ** -0.5 if gated else 1.0, 1.0 if gated else D ** -0.5
     slots = {0: 2, 1: 0, 2: 3}
     floats = ops.memory_slot_floats(H, D, E, tile)
-    states = {mode: torch.zeros(4, floats, dtype=torch.float32, device="cuda") for mode in (False, True)}
+    states = {mode: torch.zeros(4, floats, dtype=torch.float32, device="cuda") for mode in (False, True, "pieces")}
     plain_state = {(r, h): (np.zeros((D, E)), np.zeros(D), 0.0) for r in rows for h in range(H)}
     at = {r: 0 for r in rows}
     for step in range(3):
@@ -172,16 +172,21 @@ def test_matrix_memories_row_by_row_and_in_pieces(gated, H, D, E, tile):
                 o, S, nv, m = plain_memory(q * qs, k * ks, v, x[:, 2 * H * D + H * E + h], x[:, 2 * H * D + H * E + H + h], None if gated else float(decay[h]), cap, S, nv, m)
                 plain_state[(r, h)] = (S, nv, m)
                 want[q_start[i]:q_start[i + 1], h * E:(h + 1) * E] = o
-        for chunked in (False, True):
+        for chunked in (False, True, "pieces"):
             out = torch.full((proj.shape[0], H * E), float("nan"), dtype=torch.float32, device="cuda")
-            ops.matrix_memory(dev(proj, torch.float32), 0, H * D, 2 * H * D, 2 * H * D + H * E if gated else None, 2 * H * D + H * E + H if gated else None,
-                              None if gated else dev(decay, torch.float32), dev(freq, torch.float32) if rot else None, rot, dev(pos), dev(q_start),
-                              dev(np.array([slots[r] for r in live], dtype=np.int32)), states[chunked], out, H, D, E, tile, qs, ks, cap, chunked)
+            args = (dev(proj, torch.float32), 0, H * D, 2 * H * D, 2 * H * D + H * E if gated else None, 2 * H * D + H * E + H if gated else None,
+                    None if gated else dev(decay, torch.float32), dev(freq, torch.float32) if rot else None, rot, dev(pos), dev(q_start),
+                    dev(np.array([slots[r] for r in live], dtype=np.int32)), states[chunked], out, H, D, E, tile, qs, ks, cap)
+            if chunked == "pieces":
+                ops.matrix_memory_pieces(*args)
+            else:
+                ops.matrix_memory(*args, chunked)
             err = np.abs(host(out) - want).max() / max(np.abs(want).max(), 1e-30)
-            assert err < 5e-5, f"step {step}, {'pieces' if chunked else 'rows'}: {err:.2e}"
+            assert err < 5e-5, f"step {step}, {chunked}: {err:.2e}"
         for r in live:
             at[r] = cuts[r][step]
-    assert float((states[False] - states[True]).abs().max()) < 1e-3 * float(states[False].abs().max())
+    for other in (True, "pieces"):
+        assert float((states[False] - states[other]).abs().max()) < 1e-3 * float(states[False].abs().max())
     assert float(states[False][1].abs().max()) == 0.0           # the slot no request used
 
 
