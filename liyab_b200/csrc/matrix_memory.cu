@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
             const float* q_row = a.q + (size_t)(p0 + t) * a.ld + (size_t)h * D;
             const float* k_row = a.k + (size_t)(p0 + t) * a.ld + (size_t)h * D;
             for (int d = lane; d < D; d += 32) {
-                cp_async4(qs + t * LDQ + d, q_row + d);
+                if (MODE != 1) cp_async4(qs + t * LDQ + d, q_row + d);       // a piece's own sum needs no queries
                 cp_async4(ks + t * LDQ + d, k_row + d);
             }
             const float* v_row = a.v + (size_t)(p0 + t) * a.ld + (size_t)h * E + nv * VT;
@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
                 for (int d = lane; d < half; d += 32) {
                     float sn, cs;
                     sincosf((float)pos_s[t] * a.freq[d], &sn, &cs);
-                    const float ql = q_row[d], qh = q_row[d + half], kl = k_row[d], kh = k_row[d + half];
+                    const float ql = MODE != 1 ? q_row[d] : 0.0f, qh = MODE != 1 ? q_row[d + half] : 0.0f, kl = k_row[d], kh = k_row[d + half];
                     q_row[d] = (ql * cs - qh * sn) * a.q_scale;
                     q_row[d + half] = (qh * cs + ql * sn) * a.q_scale;
                     k_row[d] = (kl * cs - kh * sn) * a.k_scale;
@@ -469,17 +469,20 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryArgs a, P
     }
     cp_async_commit();
     float m = st[count];
+    float b_next = w.scalars[((size_t)g0 * a.H + h) * 2], own_next = w.scalars[((size_t)g0 * a.H + h) * 2 + 1];
     for (int p = 0; p < pieces; ++p) {
         const int g = g0 + p;
         float* mine = buf + (p & 1) * count;
+        const float b = b_next, m_own = own_next;
         cp_async_wait_all();
         __syncthreads();
-        if (p + 1 < pieces) {
+        if (p + 1 < pieces) {              // the next piece's sum and scalars travel while this one is added
             float* next = buf + ((p + 1) & 1) * count;
             for (int i = threadIdx.x; i < count; i += blockDim.x) cp_async4(next + i, sum_of(g + 1) + i);
+            b_next = w.scalars[((size_t)(g + 1) * a.H + h) * 2];
+            own_next = w.scalars[((size_t)(g + 1) * a.H + h) * 2 + 1];
         }
         cp_async_commit();
-        const float b = w.scalars[((size_t)g * a.H + h) * 2], m_own = w.scalars[((size_t)g * a.H + h) * 2 + 1];
         const float m_new = gated ? fmaxf(b + m, m_own) : 0.0f;
         const float keep = gated ? expf(b + m - m_new) : expf(b), take = gated ? expf(m_own - m_new) : 1.0f;
         float* out = sum_of(g);
